@@ -1,0 +1,716 @@
+// Causal grouped-query flash attention for sm_100a, forward and backward,
+// on the packed projection qkv[T, (Hq + 2*Hkv) * hd] (T = B*S tokens, each
+// sequence a multiple of 128 long).  All matrix products run on tcgen05 with
+// accumulators in tensor memory; operands arrive by TMA (no multicast) in
+// 128-byte-swizzled tiles, and the probability / score-gradient tiles the
+// threads produce are written to shared memory in the same swizzled layout so
+// that they can feed the next tcgen05.mma directly.
+//
+// Forward (attn_fwd_kernel): one CTA per (128 query rows, head).  Warps 0-3
+// own one query row per thread (row == TMEM lane), warp 4 issues TMA, warp 5
+// issues MMAs.  S = Q K^T is double-buffered in TMEM so the next block's
+// scores are computed while the threads run the online softmax; each P V
+// product lands in a fresh TMEM buffer and is folded into fp32 registers with
+// the running rescale factor, so TMEM is never rewritten by threads.
+//
+// Backward (attn_bwd_kernel<MODE>): one template for both passes.
+//   MODE 0 (dQ):  stationary tile = 128 query rows of one head (Q, dO);
+//                 streams 64-row K/V tiles; accumulates dQ.
+//   MODE 1 (dKV): stationary tile = 128 key rows of one kv head (K, V);
+//                 streams 64-row Q/dO tiles of every query head in the group;
+//                 accumulates dK and dV.
+// In both, S' = X1 Y1^T and dP' = X2 Y2^T are recomputed into double-buffered
+// TMEM, threads form P' = exp(S' - lse) and dS' = P' (dP' - delta) as bf16
+// tiles in shared memory, and acc1 += dS' Y1 (acc2 += P' Y2 in MODE 1) reuses
+// the streamed tiles as MN-major operands.  Nothing is reduced with atomics,
+// so gradients are reproducible.
+//
+// Every mbarrier wait is bounded (see ptx.cuh); on expiry a status code is
+// recorded and the CTA unwinds and frees its TMEM.
+#include "attention_sm100.h"
+#include "ptx.cuh"
+
+namespace piper {
+namespace {
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Writes 32 consecutive bf16 values (given as 16 packed words) of row `row`,
+// starting at 16-byte chunk index `chunk0` (multiple of 4) of a 128-byte
+// swizzled row.  `tile` is the 1024-byte-aligned base of a [rows][128 B] tile.
+__device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int row, int chunk0,
+                                                      const uint32_t (&w)[16]) {
+  uint8_t* rbase = tile + row * 128;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int phys = (chunk0 + q) ^ (row & 7);
+    *reinterpret_cast<uint4*>(rbase + phys * 16) =
+        make_uint4(w[4 * q + 0], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  }
+}
+
+// ================================================================= forward
+constexpr int FWD_THREADS = 192;
+
+template <int HD>
+struct FwdSmem {
+  static constexpr int HALVES = HD / 64;
+  static constexpr int TILE = 128 * HD * 2;     // Q, K or V tile
+  static constexpr int P_BYTES = 128 * 128 * 2;
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = TILE;            // 2 stages
+  static constexpr int V_OFF = 3 * TILE;        // 2 stages
+  static constexpr int P_OFF = 5 * TILE;
+  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+struct FwdBars {
+  uint64_t q_full;
+  uint64_t kv_full[2], kv_empty[2];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full, p_empty;
+  uint64_t o_full[2], o_empty[2];
+  uint32_t tmem_base;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restrict__ out,
+                float* __restrict__ lse, int S, int Hq, int Hkv, float scale_log2, int* status) {
+  using L = FwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  FwdBars* bars = reinterpret_cast<FwdBars*>(smem + L::BAR_OFF);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qblk = gridDim.x - 1 - blockIdx.x;   // longest rows first
+  const int head = blockIdx.y;
+  const int b = blockIdx.z;
+  const int g = head / (Hq / Hkv);
+  const int n_blocks = qblk + 1;
+  const long long tok0 = static_cast<long long>(b) * S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->kv_full[i], 1);
+      mbar_init(&bars->kv_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_empty[i], 128);
+      mbar_init(&bars->o_full[i], 1);
+      mbar_init(&bars->o_empty[i], 128);
+    }
+    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->p_empty, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap);
+  }
+  if (warp == 5) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  const uint32_t tmem_s = tmem_base;          // 2 x 128 columns
+  const uint32_t tmem_o = tmem_base + 256;    // 2 x HD columns
+
+  if (warp == 4) {
+    // ------------------------------------------------------------- TMA
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&bars->q_full, L::TILE);
+      for (int h = 0; h < L::HALVES; ++h)
+        tma_load_2d(smem + L::Q_OFF + h * 16384, &tmap, &bars->q_full, head * HD + 64 * h,
+                    static_cast<int>(tok0) + qblk * 128);
+      int j = 0;
+      for (; j < n_blocks; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&bars->kv_empty[s], ((j >> 1) & 1) ^ 1, status)) break;
+        mbar_arrive_expect_tx(&bars->kv_full[s], 2 * L::TILE);
+        for (int h = 0; h < L::HALVES; ++h) {
+          tma_load_2d(smem + L::K_OFF + s * L::TILE + h * 16384, &tmap, &bars->kv_full[s],
+                      (Hq + g) * HD + 64 * h, static_cast<int>(tok0) + j * 128);
+          tma_load_2d(smem + L::V_OFF + s * L::TILE + h * 16384, &tmap, &bars->kv_full[s],
+                      (Hq + Hkv + g) * HD + 64 * h, static_cast<int>(tok0) + j * 128);
+        }
+      }
+      if (j < n_blocks) {
+        // Unwinding after a failed wait: let the copies already issued land
+        // before the CTA and its shared memory go away.
+        mbar_wait(&bars->q_full, 0, nullptr);
+        for (int jj = j - 1; jj >= 0 && jj >= j - 2; --jj)
+          mbar_wait(&bars->kv_full[jj & 1], (jj >> 1) & 1, nullptr);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------- MMA
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, HD, false, true);
+      const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
+      const uint32_t p_addr = smem_u32(smem + L::P_OFF);
+      bool ok = mbar_wait(&bars->q_full, 0, status);
+      for (int j = 0; j <= n_blocks && ok; ++j) {
+        if (j < n_blocks) {
+          const int s = j & 1;
+          if (!mbar_wait(&bars->kv_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+          if (!mbar_wait(&bars->s_empty[s], ((j >> 1) & 1) ^ 1, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(smem + L::K_OFF + s * L::TILE);
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+            umma_bf16_ss(tmem_s + s * 128, umma_desc_sw128(q_addr + off, 16, 1024),
+                         umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->s_full[s]);
+        }
+        if (j >= 1) {
+          const int jj = j - 1;
+          const int sb = jj & 1;
+          if (!mbar_wait(&bars->p_full, jj & 1, status)) { ok = false; break; }
+          if (!mbar_wait(&bars->o_empty[sb], ((jj >> 1) & 1) ^ 1, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(smem + L::V_OFF + sb * L::TILE);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
+            umma_bf16_ss(tmem_o + sb * HD, umma_desc_sw128(p_addr + a_off, 16, 1024),
+                         umma_desc_sw128(v_addr + ks * 2048, 16384, 1024), idesc_pv,
+                         ks > 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->p_empty);
+          umma_commit(&bars->o_full[sb]);
+          umma_commit(&bars->kv_empty[sb]);
+        }
+      }
+    }
+  } else {
+    // --------------------------------------------------- softmax + output
+    const int row = threadIdx.x;                 // 0..127 == TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    float o_acc[HD];
+#pragma unroll
+    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int s = j & 1;
+      const bool diag = (j == qblk);
+      if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tmem_s + lane_sel + s * 128;
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(ts + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float v = (diag && (c * 32 + i) > row) ? -INFINITY : __uint_as_float(r[i]);
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = fast_exp2((m_run - m_new) * scale_log2);
+      const float msc = m_new * scale_log2;
+      if (j > 0 && !mbar_wait(&bars->p_empty, (j - 1) & 1, status)) { ok = false; break; }
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(ts + c * 32, r);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p0 = fast_exp2(__uint_as_float(r[2 * i]) * scale_log2 - msc);
+          float p1 = fast_exp2(__uint_as_float(r[2 * i + 1]) * scale_log2 - msc);
+          if (diag && (c * 32 + 2 * i) > row) p0 = 0.f;
+          if (diag && (c * 32 + 2 * i + 1) > row) p1 = 0.f;
+          rs += p0 + p1;
+          w[i] = pack_bf16x2(p0, p1);
+        }
+        store_row_chunk_sw128(smem + L::P_OFF + (c / 2) * 16384, row, (c % 2) * 4, w);
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->s_empty[s]);
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->p_full);
+      if (j > 0) {
+        const int sb = (j - 1) & 1;
+        if (!mbar_wait(&bars->o_full[sb], ((j - 1) >> 1) & 1, status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t to = tmem_o + lane_sel + sb * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(to + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+        mbar_arrive(&bars->o_empty[sb]);
+      }
+      l_run = l_run * alpha + rs;
+      m_run = m_new;
+      alpha_prev = alpha;
+    }
+    if (ok) {
+      const int jj = n_blocks - 1;
+      const int sb = jj & 1;
+      if (mbar_wait(&bars->o_full[sb], (jj >> 1) & 1, status)) {
+        tc_fence_after();
+        const uint32_t to = tmem_o + lane_sel + sb * HD;
+        const float inv = 1.f / l_run;
+        const long long tok = tok0 + static_cast<long long>(qblk) * 128 + row;
+        __nv_bfloat16* orow = out + tok * (static_cast<long long>(Hq) * HD) + head * HD;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(to + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int e = v * 8 + 2 * i;
+              const float a = (o_acc[c * 32 + e] * alpha_prev + __uint_as_float(r[e])) * inv;
+              const float bb = (o_acc[c * 32 + e + 1] * alpha_prev + __uint_as_float(r[e + 1])) * inv;
+              ow[i] = pack_bf16x2(a, bb);
+            }
+            reinterpret_cast<uint4*>(orow + c * 32)[v] = o;
+          }
+        }
+        lse[(static_cast<long long>(b) * Hq + head) * S + qblk * 128 + row] =
+            m_run * (scale_log2 * 0.6931471805599453f) + logf(l_run);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ================================================================ backward
+// delta[b, h, s] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (t, h).
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                  float* __restrict__ delta, long long T, int S, int Hq, int HD) {
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= T * Hq) return;
+  const long long t = gw / Hq;
+  const int h = static_cast<int>(gw % Hq);
+  const __nv_bfloat16* a = o + gw * HD;
+  const __nv_bfloat16* bb = d_o + gw * HD;
+  float s = 0.f;
+  for (int i = lane; i < HD; i += 32) s += __bfloat162float(a[i]) * __bfloat162float(bb[i]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[((t / S) * Hq + h) * S + (t % S)] = s;
+}
+
+constexpr int BWD_THREADS = 192;
+
+template <int HD>
+struct BwdSmem {
+  static constexpr int HALVES = HD / 64;
+  static constexpr int X_TILE = 128 * HD * 2;      // stationary tile
+  static constexpr int Y_TILE = 64 * HD * 2;       // streamed tile
+  static constexpr int Y_HALF = 64 * 128;          // one 64x64 box
+  static constexpr int PT_BYTES = 128 * 64 * 2;    // P' or dS' tile (one swizzle row per row)
+  static constexpr int X1_OFF = 0;
+  static constexpr int X2_OFF = X_TILE;
+  static constexpr int Y_OFF = 2 * X_TILE;         // 2 stages x (Y1, Y2)
+  static constexpr int P_OFF = Y_OFF + 4 * Y_TILE;
+  static constexpr int DS_OFF = P_OFF + PT_BYTES;
+  static constexpr int VEC_OFF = DS_OFF + PT_BYTES;  // 2 stages x (lse[64], delta[64]) floats
+  static constexpr int BAR_OFF = VEC_OFF + 2 * 2 * 64 * 4;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+struct BwdBars {
+  uint64_t x_full;
+  uint64_t y_full[2], y_empty[2];
+  uint64_t s_full[2], s_empty[2];     // S' and dP' pair
+  uint64_t t_full, t_empty;           // P'/dS' shared-memory tiles
+  uint64_t v_full[2];                 // per-column lse/delta vectors (MODE 1)
+  uint64_t acc_full;
+  uint32_t tmem_base;
+};
+
+// MODE 0: dQ.  MODE 1: dK, dV.
+template <int HD, int MODE>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 128} over packed qkv
+                const __grid_constant__ CUtensorMap tmap_qkv_y,   // box {64, 64}  over packed qkv
+                const __grid_constant__ CUtensorMap tmap_do_x,    // box {64, 128} over dO [T, Hq*hd]
+                const __grid_constant__ CUtensorMap tmap_do_y,    // box {64, 64}  over dO
+                const float* __restrict__ lse, const float* __restrict__ delta,
+                __nv_bfloat16* __restrict__ d_qkv, int S, int Hq, int Hkv, float scale,
+                float scale_log2, int* status) {
+  using L = BwdSmem<HD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  BwdBars* bars = reinterpret_cast<BwdBars*>(smem + L::BAR_OFF);
+  float* vec = reinterpret_cast<float*>(smem + L::VEC_OFF);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int group = Hq / Hkv;
+  const int b = blockIdx.z;
+  const long long tok0 = static_cast<long long>(b) * S;
+  const int W = (Hq + 2 * Hkv) * HD;   // packed row width
+
+  // Stationary block index and iteration space.
+  //   MODE 0: blockIdx.y = query head; streams kv tiles i in [0, 2*xb + 1].
+  //   MODE 1: blockIdx.y = kv head; for each query head of the group streams
+  //           q tiles i in [2*xb, S/64 - 1].
+  const int xb = (MODE == 0) ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int hy = blockIdx.y;
+  const int g = (MODE == 0) ? hy / group : hy;
+  const int tiles_per_head = (MODE == 0) ? (2 * xb + 2) : (S / 64 - 2 * xb);
+  const int n_iter = (MODE == 0) ? tiles_per_head : tiles_per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->x_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->y_full[i], 1);
+      mbar_init(&bars->y_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_empty[i], 128);
+      mbar_init(&bars->v_full[i], 64);
+    }
+    mbar_init(&bars->t_full, 128);
+    mbar_init(&bars->t_empty, 1);
+    mbar_init(&bars->acc_full, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_qkv_x);
+    tma_prefetch_desc(&tmap_qkv_y);
+    tma_prefetch_desc(&tmap_do_x);
+    tma_prefetch_desc(&tmap_do_y);
+  }
+  if (warp == 5) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  // columns: [0,64) S'0  [64,128) dP'0  [128,192) S'1  [192,256) dP'1
+  //          [256,256+HD) acc1   [384,384+HD) acc2
+  const uint32_t tmem_acc1 = tmem_base + 256;
+  const uint32_t tmem_acc2 = tmem_base + 384;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------- TMA
+    if (lane == 0) {
+      const int xrow = static_cast<int>(tok0) + xb * 128;
+      mbar_arrive_expect_tx(&bars->x_full, 2 * L::X_TILE);
+      for (int h = 0; h < L::HALVES; ++h) {
+        if (MODE == 0) {
+          tma_load_2d(smem + L::X1_OFF + h * 16384, &tmap_qkv_x, &bars->x_full, hy * HD + 64 * h, xrow);
+          tma_load_2d(smem + L::X2_OFF + h * 16384, &tmap_do_x, &bars->x_full, hy * HD + 64 * h, xrow);
+        } else {
+          tma_load_2d(smem + L::X1_OFF + h * 16384, &tmap_qkv_x, &bars->x_full,
+                      (Hq + g) * HD + 64 * h, xrow);
+          tma_load_2d(smem + L::X2_OFF + h * 16384, &tmap_qkv_x, &bars->x_full,
+                      (Hq + Hkv + g) * HD + 64 * h, xrow);
+        }
+      }
+      int it = 0;
+      for (; it < n_iter; ++it) {
+        const int st = it & 1;
+        if (!mbar_wait(&bars->y_empty[st], ((it >> 1) & 1) ^ 1, status)) break;
+        const int hh = (MODE == 0) ? hy : g * group + it / tiles_per_head;   // query head
+        const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;      // streamed tile index
+        const int yrow = static_cast<int>(tok0) + ti * 64;
+        uint8_t* y1 = smem + L::Y_OFF + st * 2 * L::Y_TILE;
+        uint8_t* y2 = y1 + L::Y_TILE;
+        mbar_arrive_expect_tx(&bars->y_full[st], 2 * L::Y_TILE);
+        for (int h = 0; h < L::HALVES; ++h) {
+          if (MODE == 0) {
+            tma_load_2d(y1 + h * L::Y_HALF, &tmap_qkv_y, &bars->y_full[st], (Hq + g) * HD + 64 * h, yrow);
+            tma_load_2d(y2 + h * L::Y_HALF, &tmap_qkv_y, &bars->y_full[st],
+                        (Hq + Hkv + g) * HD + 64 * h, yrow);
+          } else {
+            tma_load_2d(y1 + h * L::Y_HALF, &tmap_qkv_y, &bars->y_full[st], hh * HD + 64 * h, yrow);
+            tma_load_2d(y2 + h * L::Y_HALF, &tmap_do_y, &bars->y_full[st], hh * HD + 64 * h, yrow);
+          }
+        }
+      }
+      if (it < n_iter) {
+        // Unwinding: wait (bounded) for the copies in flight.
+        mbar_wait(&bars->x_full, 0, nullptr);
+        for (int jj = it - 1; jj >= 0 && jj >= it - 2; --jj)
+          mbar_wait(&bars->y_full[jj & 1], (jj >> 1) & 1, nullptr);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------- MMA
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, HD, false, true);
+      const uint32_t x1 = smem_u32(smem + L::X1_OFF);
+      const uint32_t x2 = smem_u32(smem + L::X2_OFF);
+      const uint32_t p_addr = smem_u32(smem + L::P_OFF);
+      const uint32_t ds_addr = smem_u32(smem + L::DS_OFF);
+      bool ok = mbar_wait(&bars->x_full, 0, status);
+      for (int it = 0; it <= n_iter && ok; ++it) {
+        if (it < n_iter) {
+          const int st = it & 1;
+          if (!mbar_wait(&bars->y_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+          if (!mbar_wait(&bars->s_empty[st], ((it >> 1) & 1) ^ 1, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
+          const uint32_t y2 = y1 + L::Y_TILE;
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
+            const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
+            umma_bf16_ss(tmem_base + st * 128, umma_desc_sw128(x1 + xo, 16, 1024),
+                         umma_desc_sw128(y1 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          }
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
+            const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
+            umma_bf16_ss(tmem_base + st * 128 + 64, umma_desc_sw128(x2 + xo, 16, 1024),
+                         umma_desc_sw128(y2 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->s_full[st]);
+        }
+        if (it >= 1) {
+          const int jt = it - 1;
+          const int st = jt & 1;
+          if (!mbar_wait(&bars->t_full, jt & 1, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
+          const uint32_t y2 = y1 + L::Y_TILE;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {   // contraction over the 64 streamed rows
+            umma_bf16_ss(tmem_acc1, umma_desc_sw128(ds_addr + ks * 32, 16, 1024),
+                         umma_desc_sw128(y1 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
+                         (jt > 0 || ks > 0) ? 1u : 0u);
+          }
+          if (MODE == 1) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              umma_bf16_ss(tmem_acc2, umma_desc_sw128(p_addr + ks * 32, 16, 1024),
+                           umma_desc_sw128(y2 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
+                           (jt > 0 || ks > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(&bars->t_empty);
+          umma_commit(&bars->y_empty[st]);
+          if (jt == n_iter - 1) umma_commit(&bars->acc_full);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------- P' / dS' tiles + epilogue
+    const int row = threadIdx.x;   // stationary row == TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int xpos = xb * 128 + row;   // position of this row inside the sequence
+    float row_lse = 0.f, row_delta = 0.f;
+    if (MODE == 0) {
+      const long long idx = (static_cast<long long>(b) * Hq + hy) * S + xpos;
+      row_lse = lse[idx] * 1.4426950408889634f;
+      row_delta = delta[idx];
+    }
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+      const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;
+      if (MODE == 1) {
+        // Per-column lse/delta of the streamed query tile -> shared memory.
+        const int hh = g * group + it / tiles_per_head;
+        if (row < 64) {
+          const long long idx = (static_cast<long long>(b) * Hq + hh) * S + ti * 64 + row;
+          vec[st * 128 + row] = lse[idx] * 1.4426950408889634f;
+          vec[st * 128 + 64 + row] = delta[idx];
+          mbar_arrive(&bars->v_full[st]);
+        }
+        // Bounded wait instead of a named barrier: a thread that gave up on
+        // an earlier wait must not strand the others here.
+        if (!mbar_wait(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+      }
+      if (!mbar_wait(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+      tc_fence_after();
+      if (it > 0 && !mbar_wait(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
+      // Causal mask is needed only where the streamed tile overlaps the
+      // stationary rows: element (x row, y col) is kept iff key <= query.
+      const int ypos0 = ti * 64;
+      const bool need_mask = (MODE == 0) ? (ypos0 + 63 > xb * 128) : (ypos0 < xb * 128 + 127);
+      const uint32_t ts = tmem_base + lane_sel + st * 128;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(ts + c * 32, sv);
+        tmem_ld_32x32(ts + 64 + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pw[16], dw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float p[2], d[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = c * 32 + 2 * i + e;
+            const float l2 = (MODE == 0) ? row_lse : vec[st * 128 + col];
+            const float dl = (MODE == 0) ? row_delta : vec[st * 128 + 64 + col];
+            float pv = fast_exp2(__uint_as_float(sv[2 * i + e]) * scale_log2 - l2);
+            if (need_mask) {
+              const int qpos = (MODE == 0) ? xpos : ypos0 + col;
+              const int kpos = (MODE == 0) ? ypos0 + col : xpos;
+              if (kpos > qpos) pv = 0.f;
+            }
+            p[e] = pv;
+            d[e] = pv * (__uint_as_float(dv[2 * i + e]) - dl);
+          }
+          pw[i] = pack_bf16x2(p[0], p[1]);
+          dw[i] = pack_bf16x2(d[0], d[1]);
+        }
+        if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
+        store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
+      }
+      tc_fence_before();
+      mbar_arrive(&bars->s_empty[st]);
+      fence_proxy_async_smem();
+      mbar_arrive(&bars->t_full);
+    }
+    if (ok && mbar_wait(&bars->acc_full, 0, status)) {
+      tc_fence_after();
+      const long long tok = tok0 + xpos;
+      // MODE 0 writes dQ of head hy; MODE 1 writes dK and dV of kv head g.
+      __nv_bfloat16* o1 = d_qkv + tok * W + ((MODE == 0) ? hy * HD : (Hq + g) * HD);
+      __nv_bfloat16* o2 = d_qkv + tok * W + (Hq + Hkv + g) * HD;
+#pragma unroll 1
+      for (int a = 0; a < (MODE == 0 ? 1 : 2); ++a) {
+        const uint32_t ta = (a == 0 ? tmem_acc1 : tmem_acc2) + lane_sel;
+        __nv_bfloat16* orow = (a == 0) ? o1 : o2;
+        const float sc = (a == 0) ? scale : 1.f;
+#pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(ta + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              ow[i] = pack_bf16x2(__uint_as_float(r[v * 8 + 2 * i]) * sc,
+                                  __uint_as_float(r[v * 8 + 2 * i + 1]) * sc);
+            reinterpret_cast<uint4*>(orow + c * 32)[v] = o;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess
+             ? 0
+             : -2;
+}
+
+}  // namespace
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+int attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int Hq, int Hkv, int hd,
+             float softmax_scale, int* status, cudaStream_t st) {
+  if (S % 128 != 0 || Hq % Hkv != 0 || (hd != 64 && hd != 128)) return -1;
+  if (B == 0) return 0;
+  const long long T = static_cast<long long>(B) * S;
+  const uint64_t W = static_cast<uint64_t>(Hq + 2 * Hkv) * hd;
+  CUtensorMap tm;
+  int rc = make_tmap_2d_bf16(&tm, qkv, W, T, W * 2, 64, 128);
+  if (rc != 0) return rc;
+  const float scale_log2 = softmax_scale * 1.4426950408889634f;
+  dim3 grid(S / 128, Hq, B);
+  if (hd == 128) {
+    static bool cfg = false;
+    if (!cfg) { if (set_smem(attn_fwd_kernel<128>, FwdSmem<128>::TOTAL)) return -2; cfg = true; }
+    attn_fwd_kernel<128><<<grid, FWD_THREADS, FwdSmem<128>::TOTAL, st>>>(
+        tm, static_cast<__nv_bfloat16*>(out), lse, S, Hq, Hkv, scale_log2, status);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { if (set_smem(attn_fwd_kernel<64>, FwdSmem<64>::TOTAL)) return -2; cfg = true; }
+    attn_fwd_kernel<64><<<grid, FWD_THREADS, FwdSmem<64>::TOTAL, st>>>(
+        tm, static_cast<__nv_bfloat16*>(out), lse, S, Hq, Hkv, scale_log2, status);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+template <int HD>
+static int attn_bwd_impl(const void* qkv, const void* out, const void* d_out, const float* lse,
+                         float* delta, void* d_qkv, int B, int S, int Hq, int Hkv, float softmax_scale,
+                         int* status, cudaStream_t st) {
+  const long long T = static_cast<long long>(B) * S;
+  const uint64_t W = static_cast<uint64_t>(Hq + 2 * Hkv) * HD;
+  const uint64_t Wo = static_cast<uint64_t>(Hq) * HD;
+  CUtensorMap tqx, tqy, tdx, tdy;
+  int rc;
+  if ((rc = make_tmap_2d_bf16(&tqx, qkv, W, T, W * 2, 64, 128)) != 0) return rc;
+  if ((rc = make_tmap_2d_bf16(&tqy, qkv, W, T, W * 2, 64, 64)) != 0) return rc;
+  if ((rc = make_tmap_2d_bf16(&tdx, d_out, Wo, T, Wo * 2, 64, 128)) != 0) return rc;
+  if ((rc = make_tmap_2d_bf16(&tdy, d_out, Wo, T, Wo * 2, 64, 64)) != 0) return rc;
+  static bool cfg = false;
+  if (!cfg) {
+    if (set_smem(attn_bwd_kernel<HD, 0>, BwdSmem<HD>::TOTAL)) return -2;
+    if (set_smem(attn_bwd_kernel<HD, 1>, BwdSmem<HD>::TOTAL)) return -2;
+    cfg = true;
+  }
+  const long long warps = T * Hq;
+  attn_delta_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out), delta, T, S, Hq, HD);
+  const float scale_log2 = softmax_scale * 1.4426950408889634f;
+  attn_bwd_kernel<HD, 0><<<dim3(S / 128, Hq, B), BWD_THREADS, BwdSmem<HD>::TOTAL, st>>>(
+      tqx, tqy, tdx, tdy, lse, delta, static_cast<__nv_bfloat16*>(d_qkv), S, Hq, Hkv, softmax_scale,
+      scale_log2, status);
+  attn_bwd_kernel<HD, 1><<<dim3(S / 128, Hkv, B), BWD_THREADS, BwdSmem<HD>::TOTAL, st>>>(
+      tqx, tqy, tdx, tdy, lse, delta, static_cast<__nv_bfloat16*>(d_qkv), S, Hq, Hkv, softmax_scale,
+      scale_log2, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,
+             void* d_qkv, int B, int S, int Hq, int Hkv, int hd, float softmax_scale, int* status,
+             cudaStream_t st) {
+  if (S % 128 != 0 || Hq % Hkv != 0 || (hd != 64 && hd != 128)) return -1;
+  if (B == 0) return 0;
+  if (hd == 128)
+    return attn_bwd_impl<128>(qkv, out, d_out, lse, delta, d_qkv, B, S, Hq, Hkv, softmax_scale, status, st);
+  return attn_bwd_impl<64>(qkv, out, d_out, lse, delta, d_qkv, B, S, Hq, Hkv, softmax_scale, status, st);
+}
+
+}  // namespace piper

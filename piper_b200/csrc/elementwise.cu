@@ -1,0 +1,682 @@
+// Memory-bound kernels of the transformer block for sm_100a: RMSNorm
+// (optionally fused with the residual add), QK-norm + RoPE on the packed QKV
+// projection, SwiGLU, embedding gather / scatter-add, row-wise cross-entropy
+// with in-place gradient, and the flat-buffer Adam update.  All of them move
+// 16-byte vectors and keep fp32 math in registers; none allocates.
+#include "elementwise.h"
+
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace piper {
+namespace {
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const bf16x8& p, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+__device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
+  bf16x8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) scratch[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? scratch[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (l == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) scratch[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < THREADS / 32) ? scratch[threadIdx.x] : -INFINITY;
+  if (w == 0) {
+    t = warp_max(t);
+    if (l == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One CTA per row.  Optional residual: h = x + res is written to h_out and
+// normalised, so the block's "x = x + f(norm(x))" costs one pass.
+constexpr int NORM_THREADS = 256;
+
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd, int D, float eps) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+  const bf16x8* rr = res ? reinterpret_cast<const bf16x8*>(res + row * D) : nullptr;
+  bf16x8* hr = h_out ? reinterpret_cast<bf16x8*>(h_out + row * D) : nullptr;
+  const int nvec = D / 8;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += NORM_THREADS) {
+    float f[8];
+    unpack8(xr[i], f);
+    if (rr) {
+      float g[8];
+      unpack8(rr[i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
+      // Round the residual stream to bf16 before it is normalised, so that
+      // forward and backward see the same values.
+      const bf16x8 hp = pack8(f);
+      hr[i] = hp;
+      unpack8(hp, f);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+  }
+  ss = block_sum<NORM_THREADS>(ss, scratch);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0) rstd[row] = r;
+  const bf16x8* src = rr ? reinterpret_cast<const bf16x8*>(h_out + row * D) : xr;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+  for (int i = threadIdx.x; i < nvec; i += NORM_THREADS) {
+    float f[8], g[8];
+    unpack8(src[i], f);
+    unpack8(wr[i], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = f[j] * r * g[j];
+    yr[i] = pack8(f);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)), plus an optional pass-through
+// gradient dres added to dx (the residual branch).  Column sums of dy*xhat
+// go to dw_partial[blockIdx.x][D]; a second kernel reduces them in a fixed
+// order, so the weight gradient is reproducible.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                   float* __restrict__ dw_partial, int T, int D) {
+  extern __shared__ float dw_acc[];   // D floats
+  __shared__ float scratch[32];
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) dw_acc[i] = 0.f;
+  __syncthreads();
+  const int nvec = D / 8;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  for (long long row = blockIdx.x; row < T; row += gridDim.x) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + row * D);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+    const float r = rstd[row];
+    float dot = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += NORM_THREADS) {
+      float a[8], b[8], g[8];
+      unpack8(dyr[i], a);
+      unpack8(xr[i], b);
+      unpack8(wr[i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += a[j] * g[j] * b[j] * r;
+    }
+    dot = block_sum<NORM_THREADS>(dot, scratch) / D;
+    const bf16x8* drr = dres ? reinterpret_cast<const bf16x8*>(dres + row * D) : nullptr;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
+    for (int i = threadIdx.x; i < nvec; i += NORM_THREADS) {
+      float a[8], b[8], g[8], o[8];
+      unpack8(dyr[i], a);
+      unpack8(xr[i], b);
+      unpack8(wr[i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float xhat = b[j] * r;
+        o[j] = r * (a[j] * g[j] - xhat * dot);
+        dw_acc[i * 8 + j] += a[j] * xhat;   // column owned by this thread
+      }
+      if (drr) {
+        float e[8];
+        unpack8(drr[i], e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += e[j];
+      }
+      dxr[i] = pack8(o);
+    }
+  }
+  __syncthreads();
+  float* out = dw_partial + static_cast<long long>(blockIdx.x) * D;
+  for (int i = threadIdx.x; i < D; i += NORM_THREADS) out[i] = dw_acc[i];
+}
+
+// dw[c] (+)= sum_b partial[b][c]; fp32 output (the flat gradient bucket) or
+// bf16 when dw_is_bf16.
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int D,
+                                       float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
+                                       int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<long long>(b) * D + c];
+  if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + s : s;
+  if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + s : s);
+}
+
+// --------------------------------------------------------- QK-norm + RoPE
+// qkv is the packed projection [T, (Hq + 2*Hkv) * hd].  One warp handles one
+// (token, head) vector of hd = 128 or 64 elements; v heads are copied.
+// rope pairs: interleaved (x[2i], x[2i+1]) or half-split (x[i], x[i+hd/2]).
+// cos/sin are fp32 [S, hd/2]; position of token t is t % S.
+template <int HD>
+__global__ void qk_rope_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                               const float* __restrict__ cosp, const float* __restrict__ sinp,
+                               const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                               float* __restrict__ rstd_out, long long T, int S, int Hq, int Hkv,
+                               int interleaved, float eps, float sin_sign) {
+  constexpr int PER = HD / 32;   // elements per lane (4 or 2)
+  const int heads = Hq + 2 * Hkv;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= T * heads) return;
+  const long long t = gw / heads;
+  const int h = static_cast<int>(gw % heads);
+  const __nv_bfloat16* src = in + gw * HD;
+  __nv_bfloat16* dst = out + gw * HD;
+  // Lane owns PER consecutive elements in the interleaved form, or elements
+  // {j, j+HD/2} pairs in the half-split form.
+  float v[PER];
+  int idx[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (interleaved) idx[j] = lane * PER + j;
+    else idx[j] = (j & 1) * (HD / 2) + lane * (PER / 2) + (j >> 1);
+    v[j] = __bfloat162float(src[idx[j]]);
+  }
+  if (h >= Hq + Hkv) {   // value head: plain copy
+#pragma unroll
+    for (int j = 0; j < PER; ++j) dst[idx[j]] = __float2bfloat16(v[j]);
+    return;
+  }
+  const __nv_bfloat16* nw = (h < Hq) ? qw : kw;
+  if (nw != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) ss += v[j] * v[j];
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / HD + eps);
+    if (rstd_out != nullptr && lane == 0) rstd_out[t * (Hq + Hkv) + h] = r;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) v[j] = v[j] * r * __bfloat162float(nw[idx[j]]);
+  }
+  const int pos = static_cast<int>(t % S);
+#pragma unroll
+  for (int j = 0; j < PER; j += 2) {
+    const int pair = interleaved ? (idx[j] >> 1) : idx[j];   // index into [0, HD/2)
+    const float c = cosp[static_cast<long long>(pos) * (HD / 2) + pair];
+    const float s = sin_sign * sinp[static_cast<long long>(pos) * (HD / 2) + pair];
+    const float a = v[j], b = v[j + 1];
+    dst[idx[j]] = __float2bfloat16(a * c - b * s);
+    dst[idx[j + 1]] = __float2bfloat16(a * s + b * c);
+  }
+}
+
+// Backward of QK-norm + RoPE: un-rotate the incoming gradient (RoPE is an
+// orthogonal map, so its transpose is the rotation by -theta), then apply the
+// RMSNorm backward per head; weight-gradient contributions are atomically
+// added to fp32 dqw/dkw (hd values each, negligible traffic).
+template <int HD>
+__global__ void qk_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
+                                   const __nv_bfloat16* __restrict__ in /*pre-norm qkv*/,
+                                   __nv_bfloat16* __restrict__ din, const float* __restrict__ cosp,
+                                   const float* __restrict__ sinp, const __nv_bfloat16* __restrict__ qw,
+                                   const __nv_bfloat16* __restrict__ kw, float* __restrict__ dqw,
+                                   float* __restrict__ dkw, long long T, int S, int Hq, int Hkv,
+                                   int interleaved, float eps) {
+  constexpr int PER = HD / 32;
+  const int heads = Hq + 2 * Hkv;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= T * heads) return;
+  const long long t = gw / heads;
+  const int h = static_cast<int>(gw % heads);
+  const __nv_bfloat16* g = dout + gw * HD;
+  __nv_bfloat16* dst = din + gw * HD;
+  float d[PER];
+  int idx[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (interleaved) idx[j] = lane * PER + j;
+    else idx[j] = (j & 1) * (HD / 2) + lane * (PER / 2) + (j >> 1);
+    d[j] = __bfloat162float(g[idx[j]]);
+  }
+  if (h >= Hq + Hkv) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) dst[idx[j]] = __float2bfloat16(d[j]);
+    return;
+  }
+  const int pos = static_cast<int>(t % S);
+#pragma unroll
+  for (int j = 0; j < PER; j += 2) {
+    const int pair = interleaved ? (idx[j] >> 1) : idx[j];
+    const float c = cosp[static_cast<long long>(pos) * (HD / 2) + pair];
+    const float s = sinp[static_cast<long long>(pos) * (HD / 2) + pair];
+    const float a = d[j], b = d[j + 1];
+    d[j] = a * c + b * s;
+    d[j + 1] = -a * s + b * c;
+  }
+  const __nv_bfloat16* nw = (h < Hq) ? qw : kw;
+  if (nw != nullptr) {
+    const __nv_bfloat16* src = in + gw * HD;
+    float x[PER], wv[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      x[j] = __bfloat162float(src[idx[j]]);
+      wv[j] = __bfloat162float(nw[idx[j]]);
+      ss += x[j] * x[j];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / HD + eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) dot += d[j] * wv[j] * x[j] * r;
+    dot = warp_sum(dot) / HD;
+    float* dwp = (h < Hq) ? dqw : dkw;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const float xhat = x[j] * r;
+      if (dwp != nullptr) atomicAdd(dwp + idx[j], d[j] * xhat);
+      d[j] = r * (d[j] * wv[j] - xhat * dot);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) dst[idx[j]] = __float2bfloat16(d[j]);
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// h13 = [gate | up] of width 2F per row; act = silu(gate) * up.
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ act,
+                                  long long T, int F) {
+  const long long nvec = T * (F / 8);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / (F / 8);
+    const int c = static_cast<int>(i % (F / 8));
+    const bf16x8* base = reinterpret_cast<const bf16x8*>(h13 + row * 2 * F);
+    float g[8], u[8], o[8];
+    unpack8(base[c], g);
+    unpack8(base[F / 8 + c], u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    reinterpret_cast<bf16x8*>(act + row * F)[c] = pack8(o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ h13, const __nv_bfloat16* __restrict__ dact,
+                                  __nv_bfloat16* __restrict__ dh13, long long T, int F) {
+  const long long nvec = T * (F / 8);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / (F / 8);
+    const int c = static_cast<int>(i % (F / 8));
+    const bf16x8* base = reinterpret_cast<const bf16x8*>(h13 + row * 2 * F);
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(base[c], g);
+    unpack8(base[F / 8 + c], u);
+    unpack8(reinterpret_cast<const bf16x8*>(dact + row * F)[c], d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * sg;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
+    }
+    bf16x8* ob = reinterpret_cast<bf16x8*>(dh13 + row * 2 * F);
+    ob[c] = pack8(dg);
+    ob[F / 8 + c] = pack8(du);
+  }
+}
+
+// ---------------------------------------------------------------- embedding
+__global__ void embedding_fwd_kernel(const long long* __restrict__ tokens,
+                                     const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
+                                     long long T, int D, int V, int* status) {
+  const long long row = blockIdx.x;
+  long long tok = tokens[row];
+  if (tok < 0 || tok >= V) {   // recorded, not trapped
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 3);
+    tok = 0;
+  }
+  const bf16x8* src = reinterpret_cast<const bf16x8*>(table + tok * D);
+  bf16x8* dst = reinterpret_cast<bf16x8*>(out + row * D);
+  for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// dtable[tok] += dout[row]; fp32 atomics straight into the gradient bucket.
+__global__ void embedding_bwd_kernel(const long long* __restrict__ tokens,
+                                     const __nv_bfloat16* __restrict__ dout, float* __restrict__ dtable,
+                                     long long T, int D, int V) {
+  const long long row = blockIdx.x;
+  const long long tok = tokens[row];
+  if (tok < 0 || tok >= V) return;
+  const __nv_bfloat16* src = dout + row * D;
+  float* dst = dtable + tok * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(dst + i, __bfloat162float(src[i]));
+}
+
+// ------------------------------------------------------------ cross-entropy
+// One CTA per row of bf16 logits [T, V]: online max / sum-exp, per-token loss
+// and log-sum-exp.  ignore_index rows produce loss 0.
+constexpr int CE_THREADS = 512;
+
+__global__ void __launch_bounds__(CE_THREADS)
+ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
+              float* __restrict__ loss, float* __restrict__ lse, int V, long long ld,
+              long long ignore_index) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  const int nvec = V / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(lr)[i], f);
+    float lm = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+    if (lm > m) {
+      s *= __expf(m - lm);
+      m = lm;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) {
+    const float f = __bfloat162float(lr[i]);
+    if (f > m) {
+      s *= __expf(m - f);
+      m = f;
+    }
+    s += __expf(f - m);
+  }
+  const float gm = block_max<CE_THREADS>(m, scratch);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum<CE_THREADS>(s, scratch);
+  if (threadIdx.x == 0) {
+    const float l = gm + logf(gs);
+    lse[row] = l;
+    const long long y = labels[row];
+    loss[row] = (y == ignore_index || y < 0 || y >= V) ? 0.f : l - __bfloat162float(lr[y]);
+  }
+}
+
+// dlogits = (softmax - onehot) * gscale[0] * row_scale, written to `out`
+// (may alias logits).
+__global__ void __launch_bounds__(CE_THREADS)
+ce_bwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
+              const float* __restrict__ lse, const float* __restrict__ gscale, float row_scale,
+              __nv_bfloat16* __restrict__ out, int V, long long ld, long long ignore_index) {
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* lr = logits + row * ld;
+  __nv_bfloat16* orow = out + row * ld;
+  const long long y = labels[row];
+  const bool ignored = (y == ignore_index || y < 0 || y >= V);
+  const float sc = ignored ? 0.f : gscale[0] * row_scale;
+  const float l = lse[row];
+  const int nvec = V / 8;
+  for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(lr)[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p = __expf(f[j] - l);
+      f[j] = (p - ((i * 8 + j) == y ? 1.f : 0.f)) * sc;
+    }
+    reinterpret_cast<bf16x8*>(orow)[i] = pack8(f);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += CE_THREADS) {
+    const float p = __expf(__bfloat162float(lr[i]) - l);
+    orow[i] = __float2bfloat16((p - (i == y ? 1.f : 0.f)) * sc);
+  }
+}
+
+// --------------------------------------------------------------------- Adam
+// Flat-buffer Adam(W): fp32 master / m / v, fp32 gradient (scaled by
+// grad_scale), bf16 parameter copy written in the same pass.
+__global__ void adam_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                                 const float* __restrict__ grad, __nv_bfloat16* __restrict__ param,
+                                 long long n, float lr, float b1, float b2, float eps, float wd,
+                                 float bc1, float bc2, float grad_scale) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float g = grad[i] * grad_scale;
+    float p = master[i];
+    const float mi = b1 * m[i] + (1.f - b1) * g;
+    const float vi = b2 * v[i] + (1.f - b2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    const float denom = sqrtf(vi / bc2) + eps;
+    p = p - lr * (mi / bc1) / denom - lr * wd * p;
+    master[i] = p;
+    if (param) param[i] = __float2bfloat16(p);
+  }
+}
+
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                        long long n, float scale) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16(in[i] * scale);
+}
+
+// acc (fp32) += g (bf16): gradient accumulation into the flat bucket for
+// parameters whose gradient comes from autograd as a bf16 tensor.
+__global__ void accum_bf16_into_f32_kernel(const __nv_bfloat16* __restrict__ g, float* __restrict__ acc,
+                                           long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    acc[i] += __bfloat162float(g[i]);
+}
+
+inline int grid_for(long long work, int threads, int max_blocks = 148 * 16) {
+  long long b = (work + threads - 1) / threads;
+  if (b > max_blocks) b = max_blocks;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace
+
+#define PIPER_LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -3)
+
+int rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd,
+                long long T, int D, float eps, cudaStream_t st) {
+  if (D % 8 != 0) return -1;
+  if (T == 0) return 0;
+  rmsnorm_fwd_kernel<<<static_cast<unsigned>(T), NORM_THREADS, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+      static_cast<__nv_bfloat16*>(h_out), rstd, D, eps);
+  return PIPER_LAUNCH_OK();
+}
+
+int rmsnorm_bwd_num_partials(long long T) {
+  const int cap = 148 * 2;
+  return static_cast<int>(T < cap ? (T > 0 ? T : 1) : cap);
+}
+
+int rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                void* dx, float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, long long T,
+                int D, cudaStream_t st) {
+  if (D % 8 != 0 || D * sizeof(float) > 160 * 1024) return -1;
+  if (T == 0) return 0;
+  const int nb = rmsnorm_bwd_num_partials(T);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    configured = true;
+  }
+  rmsnorm_bwd_kernel<<<nb, NORM_THREADS, D * sizeof(float), st>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
+      static_cast<__nv_bfloat16*>(dx), dw_partial, static_cast<int>(T), D);
+  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, nb, D, dw_f32,
+                                                         static_cast<__nv_bfloat16*>(dw_bf16), accumulate);
+  return PIPER_LAUNCH_OK();
+}
+
+int qk_rope_fwd(const void* in, void* out, const float* cosp, const float* sinp, const void* qw,
+                const void* kw, long long T, int S, int Hq, int Hkv, int hd, int interleaved, float eps,
+                cudaStream_t st) {
+  const long long warps = T * (Hq + 2 * Hkv);
+  if (warps == 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + threads - 1) / threads);
+  auto a = static_cast<const __nv_bfloat16*>(in);
+  auto o = static_cast<__nv_bfloat16*>(out);
+  auto q = static_cast<const __nv_bfloat16*>(qw);
+  auto k = static_cast<const __nv_bfloat16*>(kw);
+  if (hd == 128)
+    qk_rope_kernel<128><<<blocks, threads, 0, st>>>(a, o, cosp, sinp, q, k, nullptr, T, S, Hq, Hkv,
+                                                    interleaved, eps, 1.f);
+  else if (hd == 64)
+    qk_rope_kernel<64><<<blocks, threads, 0, st>>>(a, o, cosp, sinp, q, k, nullptr, T, S, Hq, Hkv,
+                                                   interleaved, eps, 1.f);
+  else
+    return -1;
+  return PIPER_LAUNCH_OK();
+}
+
+int qk_rope_bwd(const void* dout, const void* in, void* din, const float* cosp, const float* sinp,
+                const void* qw, const void* kw, float* dqw, float* dkw, long long T, int S, int Hq,
+                int Hkv, int hd, int interleaved, float eps, cudaStream_t st) {
+  const long long warps = T * (Hq + 2 * Hkv);
+  if (warps == 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((warps * 32 + threads - 1) / threads);
+  auto g = static_cast<const __nv_bfloat16*>(dout);
+  auto a = static_cast<const __nv_bfloat16*>(in);
+  auto o = static_cast<__nv_bfloat16*>(din);
+  auto q = static_cast<const __nv_bfloat16*>(qw);
+  auto k = static_cast<const __nv_bfloat16*>(kw);
+  if (hd == 128)
+    qk_rope_bwd_kernel<128><<<blocks, threads, 0, st>>>(g, a, o, cosp, sinp, q, k, dqw, dkw, T, S, Hq,
+                                                        Hkv, interleaved, eps);
+  else if (hd == 64)
+    qk_rope_bwd_kernel<64><<<blocks, threads, 0, st>>>(g, a, o, cosp, sinp, q, k, dqw, dkw, T, S, Hq,
+                                                       Hkv, interleaved, eps);
+  else
+    return -1;
+  return PIPER_LAUNCH_OK();
+}
+
+int swiglu_fwd(const void* h13, void* act, long long T, int F, cudaStream_t st) {
+  if (F % 8 != 0) return -1;
+  if (T == 0) return 0;
+  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(act), T, F);
+  return PIPER_LAUNCH_OK();
+}
+
+int swiglu_bwd(const void* h13, const void* dact, void* dh13, long long T, int F, cudaStream_t st) {
+  if (F % 8 != 0) return -1;
+  if (T == 0) return 0;
+  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(h13), static_cast<const __nv_bfloat16*>(dact),
+      static_cast<__nv_bfloat16*>(dh13), T, F);
+  return PIPER_LAUNCH_OK();
+}
+
+int embedding_fwd(const long long* tokens, const void* table, void* out, long long T, int D, int V,
+                  int* status, cudaStream_t st) {
+  if (D % 8 != 0) return -1;
+  if (T == 0) return 0;
+  embedding_fwd_kernel<<<static_cast<unsigned>(T), 128, 0, st>>>(
+      tokens, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), T, D, V, status);
+  return PIPER_LAUNCH_OK();
+}
+
+int embedding_bwd(const long long* tokens, const void* dout, float* dtable, long long T, int D, int V,
+                  cudaStream_t st) {
+  if (T == 0) return 0;
+  embedding_bwd_kernel<<<static_cast<unsigned>(T), 256, 0, st>>>(
+      tokens, static_cast<const __nv_bfloat16*>(dout), dtable, T, D, V);
+  return PIPER_LAUNCH_OK();
+}
+
+int ce_fwd(const void* logits, const long long* labels, float* loss, float* lse, long long T, int V,
+           long long ld, long long ignore_index, cudaStream_t st) {
+  if (ld % 8 != 0) return -1;
+  if (T == 0) return 0;
+  ce_fwd_kernel<<<static_cast<unsigned>(T), CE_THREADS, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(logits), labels, loss, lse, V, ld, ignore_index);
+  return PIPER_LAUNCH_OK();
+}
+
+int ce_bwd(const void* logits, const long long* labels, const float* lse, const float* gscale,
+           float row_scale, void* out, long long T, int V, long long ld, long long ignore_index,
+           cudaStream_t st) {
+  if (ld % 8 != 0) return -1;
+  if (T == 0) return 0;
+  ce_bwd_kernel<<<static_cast<unsigned>(T), CE_THREADS, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(logits), labels, lse, gscale, row_scale,
+      static_cast<__nv_bfloat16*>(out), V, ld, ignore_index);
+  return PIPER_LAUNCH_OK();
+}
+
+int adam_flat(float* master, float* m, float* v, const float* grad, void* param_bf16, long long n,
+              float lr, float b1, float b2, float eps, float wd, int step, float grad_scale,
+              cudaStream_t st) {
+  if (n == 0) return 0;
+  const float bc1 = 1.f - powf(b1, static_cast<float>(step));
+  const float bc2 = 1.f - powf(b2, static_cast<float>(step));
+  adam_flat_kernel<<<grid_for(n, 256), 256, 0, st>>>(master, m, v, grad,
+                                                    static_cast<__nv_bfloat16*>(param_bf16), n, lr, b1, b2,
+                                                    eps, wd, bc1, bc2, grad_scale);
+  return PIPER_LAUNCH_OK();
+}
+
+int cast_f32_to_bf16(const float* in, void* out, long long n, float scale, cudaStream_t st) {
+  if (n == 0) return 0;
+  cast_f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(in, static_cast<__nv_bfloat16*>(out), n, scale);
+  return PIPER_LAUNCH_OK();
+}
+
+int accum_bf16_into_f32(const void* g, float* acc, long long n, cudaStream_t st) {
+  if (n == 0) return 0;
+  accum_bf16_into_f32_kernel<<<grid_for(n, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(g), acc, n);
+  return PIPER_LAUNCH_OK();
+}
+
+}  // namespace piper

@@ -1,0 +1,318 @@
+// Dense bf16 GEMM for sm_100a: C[M,N] = A[M,K] * B[N,K]^T with fp32
+// accumulation in tensor memory.
+//
+// One persistent CTA per SM walks 128x256 output tiles.  Roles by warp:
+//   warp 0      TMA producer: fills a 4-stage shared-memory ring with
+//               128-byte-swizzled operand tiles (cp.async.bulk.tensor, no
+//               multicast).
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (128x256x16) into one
+//               of two 256-column TMEM accumulators and commits to mbarriers.
+//   warp 2      TMEM allocator / deallocator.
+//   warps 4-7   epilogue: tcgen05.ld the finished accumulator (32 lanes per
+//               warp), convert and store, while the MMA warp already works on
+//               the next tile in the other accumulator.
+//
+// Each operand can be K-major (contraction index contiguous in memory) or
+// MN-major (row index contiguous), which covers forward (X W^T), input
+// gradient (dY W) and weight gradient (dY^T X) of a linear layer without any
+// transposed copy.  The epilogue either stores bf16 or adds into an fp32
+// buffer (gradient accumulation into the flat fp32 bucket).
+//
+// All mbarrier waits are bounded; on expiry the kernel records a status code,
+// drains its TMA copies, frees TMEM and returns.
+#include "gemm_sm100.h"
+#include "ptx.cuh"
+
+namespace piper {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;            // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int ACC_BUFS = 2;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int MN_BOX_BYTES = 64 * BK * 2;    // one MN-major TMA box: 64 k-rows x 128 B
+constexpr int NUM_THREADS = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct Barriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[ACC_BUFS];
+  uint64_t acc_empty[ACC_BUFS];
+  uint32_t tmem_base;
+};
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            void* __restrict__ c_ptr, long long ldc, int M, int N, int K, int accumulate,
+            int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < ACC_BUFS; ++a) {
+      mbar_init(&bars->acc_full[a], 1);
+      mbar_init(&bars->acc_empty[a], 4);   // one arrive per epilogue warp
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(&bars->tmem_base, ACC_BUFS * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM;
+        const int n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, status)) { ok = false; break; }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(&bars->full[s], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * MN_BOX_BYTES, &tmap_a, &bars->full[s], m0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sa, &tmap_a, &bars->full[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * MN_BOX_BYTES, &tmap_b, &bars->full[s], n0 + 64 * j, k0);
+          } else {
+            tma_load_2d(sb, &tmap_b, &bars->full[s], k0, n0);
+          }
+        }
+      }
+      if (!ok) {
+        // Unwinding: let the copies already issued land before the CTA (and
+        // its shared memory) goes away.  Stage s was last filled by iteration
+        // it_s = largest value < it congruent to s.
+        for (int s = 0; s < STAGES; ++s) {
+          if (it <= static_cast<uint32_t>(s)) continue;
+          const uint32_t fills = (it - 1 - s) / STAGES + 1;
+          mbar_wait(&bars->full[s], (fills - 1) & 1, nullptr);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait(&bars->acc_empty[acc], acc_ph ^ 1, status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bars->full[s], ph, status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? umma_desc_sw128(sa + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
+                                     : umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
+                                     : umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->empty[s]);       // frees the smem stage when the MMAs retire
+        }
+        if (ok) umma_commit(&bars->acc_full[acc]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------- epilogue
+    const int ew = warp - 4;                  // == warp % 4: TMEM lanes [32*ew, 32*ew+32)
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      const int m0 = (tile % tiles_m) * BM;
+      const int n0 = (tile / tiles_m) * BN;
+      const int acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!mbar_wait(&bars->acc_full[acc], acc_ph, status)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + ew * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          if (EPI == kEpiStoreBf16) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(c_ptr) + row * ldc + col0;
+            if (col0 + 32 <= N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                reinterpret_cast<uint4*>(crow)[v] = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j)
+                crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          } else {
+            float* crow = reinterpret_cast<float*>(c_ptr) + row * ldc + col0;
+            if (col0 + 32 <= N) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
+                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (accumulate) {
+                  const float4 p = reinterpret_cast<const float4*>(crow)[v];
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                reinterpret_cast<float4*>(crow)[v] = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                const float x = __uint_as_float(r[j]);
+                crow[j] = accumulate ? crow[j] + x : x;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, ACC_BUFS * BN);
+  }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point, so the
+// library does not link against libcuda directly.
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r =
+      fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, int num_sms,
+                  cudaStream_t stream) {
+  auto kern = gemm_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess)
+      return -2;
+    configured = true;
+  }
+  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, g.c, g.ldc, g.M, g.N, g.K, g.accumulate,
+                                                  g.status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int gemm_bf16_launch(const GemmArgs& g, int num_sms, cudaStream_t stream) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
+  CUtensorMap ta, tb;
+  int rc;
+  // K-major operand: dims {K, rows}, box {64, tile rows}.
+  // MN-major operand: dims {rows, K}, box {64, 64}.
+  rc = g.a_mn_major ? make_tmap_2d_bf16(&ta, g.a, g.M, g.K, g.lda * 2, 64, BK)
+                    : make_tmap_2d_bf16(&ta, g.a, g.K, g.M, g.lda * 2, BK, BM);
+  if (rc != 0) return rc;
+  rc = g.b_mn_major ? make_tmap_2d_bf16(&tb, g.b, g.N, g.K, g.ldb * 2, 64, BK)
+                    : make_tmap_2d_bf16(&tb, g.b, g.K, g.N, g.ldb * 2, BK, BN);
+  if (rc != 0) return rc;
+  const int key = (g.a_mn_major ? 4 : 0) | (g.b_mn_major ? 2 : 0) | (g.epilogue == kEpiAccumF32 ? 1 : 0);
+  switch (key) {
+    case 0: return launch<false, false, kEpiStoreBf16>(g, ta, tb, num_sms, stream);
+    case 1: return launch<false, false, kEpiAccumF32>(g, ta, tb, num_sms, stream);
+    case 2: return launch<false, true, kEpiStoreBf16>(g, ta, tb, num_sms, stream);
+    case 3: return launch<false, true, kEpiAccumF32>(g, ta, tb, num_sms, stream);
+    case 4: return launch<true, false, kEpiStoreBf16>(g, ta, tb, num_sms, stream);
+    case 5: return launch<true, false, kEpiAccumF32>(g, ta, tb, num_sms, stream);
+    case 6: return launch<true, true, kEpiStoreBf16>(g, ta, tb, num_sms, stream);
+    default: return launch<true, true, kEpiAccumF32>(g, ta, tb, num_sms, stream);
+  }
+}
+
+}  // namespace piper

@@ -1,0 +1,43 @@
+// Host-side interface of the tcgen05 GEMM family (gemm_sm100.cu,
+// grouped_gemm_sm100.cu).  Plain C++ / CUDA runtime types only, so the
+// kernels build without any framework headers.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace piper {
+
+enum : int {
+  kEpiStoreBf16 = 0,   // C (bf16) = acc
+  kEpiAccumF32 = 1,    // C (fp32) = acc, or C += acc when accumulate != 0
+};
+
+// C[M,N] = A[M,K] * B[N,K]^T.
+//   a_mn_major == 0: A is stored row-major [M, K] with row stride lda (elements).
+//   a_mn_major == 1: A is stored row-major [K, M] with row stride lda.
+//   b_mn_major == 0: B is stored row-major [N, K] with row stride ldb.
+//   b_mn_major == 1: B is stored row-major [K, N] with row stride ldb.
+// Base pointers must be 16-byte aligned and lda/ldb multiples of 8 elements
+// (TMA global-stride rule); ldc is in elements of the output type.
+struct GemmArgs {
+  const void* a;
+  const void* b;
+  void* c;
+  long long lda, ldb, ldc;
+  int M, N, K;
+  int a_mn_major, b_mn_major;
+  int epilogue;     // kEpi*
+  int accumulate;   // only for kEpiAccumF32
+  int* status;      // device int, 0 = ok (see ptx.cuh)
+};
+
+// Returns 0 on success, a negative code for a launch/set-up failure, or the
+// CUresult of a failed tensor-map encode.
+int gemm_bf16_launch(const GemmArgs& args, int num_sms, cudaStream_t stream);
+
+// Encodes a 2-D bf16 tensor map with 128-byte swizzle.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                      uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);
+
+}  // namespace piper

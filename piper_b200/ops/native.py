@@ -1,0 +1,90 @@
+"""Loading of the native sm_100a library and the per-device status word.
+
+``lib()`` returns ``torch.ops.piper_c`` after loading
+``piper_b200/lib/libpiper_b200.so``.  On a machine with a GPU a missing
+library is an error (the CUDA path must never silently fall back); on a
+CPU-only machine the ops in this package use their PyTorch reference bodies
+and ``lib()`` is never reached.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libpiper_b200.so"
+_loaded = False
+_status: dict[int, torch.Tensor] = {}
+_cdll = None
+
+STATUS_MESSAGES = {
+    0: "ok",
+    1: "an mbarrier wait inside a kernel ran out of polls",
+    2: "a wait on a peer GPU's flag ran out of polls",
+    3: "a kernel rejected an argument (index out of range)",
+}
+
+
+class PiperKernelError(RuntimeError):
+    """A kernel recorded a non-zero status word (bounded wait expired, bad index)."""
+
+
+class PiperCommTimeout(PiperKernelError):
+    """A fused collective kernel gave up waiting for a peer."""
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def lib():
+    """Load the native library once and return the ``torch.ops.piper_c`` namespace."""
+    global _loaded
+    if not _loaded:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(
+                f"native library {_LIB_PATH} is missing; build it with `python -m piper_b200.build` "
+                "(CUDA tensors are never routed to a PyTorch fallback)"
+            )
+        torch.ops.load_library(str(_LIB_PATH))
+        _loaded = True
+    return torch.ops.piper_c
+
+
+def cdll() -> ctypes.CDLL:
+    """The same library through ctypes, for its exported ``extern \"C\"`` entry points."""
+    global _cdll
+    if _cdll is None:
+        lib()
+        _cdll = ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else 0)
+    return _cdll
+
+
+def status_tensor(device: torch.device | None = None) -> torch.Tensor:
+    """One int32 status word per device, shared by all kernels launched from this process."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _status[idx] = t
+    return t
+
+
+def check_status(device: torch.device | None = None, *, reset: bool = True) -> None:
+    """Synchronising read of the status word; raises if a kernel recorded a failure."""
+    if not torch.cuda.is_available():
+        return
+    t = status_tensor(device)
+    code = int(t.item())
+    if code != 0:
+        if reset:
+            t.zero_()
+        msg = STATUS_MESSAGES.get(code, f"unknown status {code}")
+        raise (PiperCommTimeout if code == 2 else PiperKernelError)(f"kernel status {code}: {msg}")

@@ -1,0 +1,197 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    from piper_b200.ops import native
+
+    yield
+    native.check_status()
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 192), (200, 328, 136), (4096, 1024, 512)])
+def test_gemm_forward_layout(M, N, K):
+    from piper_b200.ops import native
+
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    native.lib().gemm(a, b, c, False, False, False, native.status_tensor())
+    ref = a.float() @ b.float().t()
+    assert _rel_err(c, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 320), (200, 328, 136)])
+def test_gemm_dgrad_and_wgrad_layouts(M, N, K):
+    from piper_b200.ops import native
+
+    torch.manual_seed(1)
+    st = native.status_tensor()
+    # dgrad: C[M,N] = A[M,K] * Bs[K,N]  (B stored [K, N])
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    bs = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    native.lib().gemm(a, bs, c, False, True, False, st)
+    assert _rel_err(c, a.float() @ bs.float()) < 1e-2
+    # wgrad: C[M,N] = As[K,M]^T * Bs[K,N], fp32 accumulate into an existing buffer
+    as_ = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    ref = acc + as_.float().t() @ bs.float()
+    native.lib().gemm(as_, bs, acc, True, True, True, st)
+    assert _rel_err(acc, ref) < 1e-2
+    # A MN-major with B K-major
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c2 = torch.empty(M, N, device="cuda", dtype=torch.float32)
+    native.lib().gemm(as_, b, c2, True, False, False, st)
+    assert _rel_err(c2, as_.float().t() @ b.float().t()) < 1e-2
+
+
+def test_linear_op_autograd():
+    from piper_b200 import ops
+
+    torch.manual_seed(2)
+    x = torch.randn(2, 256, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(768, 512, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_(True)
+    y = ops.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("D", [256, 2048, 4096])
+def test_rmsnorm_and_residual(D):
+    from piper_b200 import ops
+
+    torch.manual_seed(3)
+    x = torch.randn(300, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(300, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y, h = ops.add_rmsnorm(x, r, w, 1e-6)
+    gy, gh = torch.randn_like(y), torch.randn_like(h)
+    torch.autograd.backward([y, h], [gy, gh])
+    xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+    hr = (xr + rr).to(torch.bfloat16).float() + 0 * (xr + rr)
+    hr = xr + rr
+    yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
+    torch.autograd.backward([yr, hr], [gy.float(), gh.float()])
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(h, hr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2 and _rel_err(r.grad, rr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+    y2 = ops.rmsnorm(x.detach(), w.detach(), 1e-6)
+    x0 = x.detach().float()
+    assert _rel_err(y2, x0 * torch.rsqrt(x0.pow(2).mean(-1, keepdim=True) + 1e-6) * w.detach().float()) < 1e-2
+
+
+@pytest.mark.parametrize("hd,inter,qknorm", [(128, True, False), (128, False, True), (64, False, False), (64, True, True)])
+def test_qk_rope(hd, inter, qknorm):
+    from piper_b200 import ops
+    from piper_b200.ops.core import _qk_rope_ref
+
+    torch.manual_seed(4)
+    S, Hq, Hkv = 64, 4, 2
+    cos, sin = ops.rope_tables(hd, S, 10000.0, device="cuda")
+    qkv = torch.randn(2 * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    qw = torch.randn(hd, device="cuda", dtype=torch.bfloat16, requires_grad=True) if qknorm else None
+    kw = torch.randn(hd, device="cuda", dtype=torch.bfloat16, requires_grad=True) if qknorm else None
+    out = ops.qk_rope(qkv, cos, sin, qw, kw, S, Hq, Hkv, hd, inter, 1e-6)
+    g = torch.randn_like(out)
+    out.backward(g)
+    q2 = qkv.detach().float().requires_grad_(True)
+    qw2 = qw.detach().float().requires_grad_(True) if qknorm else None
+    kw2 = kw.detach().float().requires_grad_(True) if qknorm else None
+    ref = _qk_rope_ref(q2, cos, sin, qw2, kw2, S, Hq, Hkv, hd, inter, 1e-6)
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 1e-2
+    assert _rel_err(qkv.grad, q2.grad) < 2e-2
+    if qknorm:
+        assert _rel_err(qw.grad, qw2.grad) < 3e-2 and _rel_err(kw.grad, kw2.grad) < 3e-2
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,hd", [(1, 128, 2, 1, 128), (2, 256, 4, 2, 128), (1, 512, 4, 4, 64), (1, 1024, 8, 2, 128)])
+def test_attention_fwd_bwd(B, S, Hq, Hkv, hd):
+    from piper_b200 import ops
+    from piper_b200.ops.core import _attention_ref
+
+    torch.manual_seed(5)
+    qkv = (torch.randn(B * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=torch.bfloat16)).requires_grad_(True)
+    out = ops.attention(qkv, B, S, Hq, Hkv, hd)
+    g = torch.randn_like(out)
+    out.backward(g)
+    q2 = qkv.detach().float().requires_grad_(True)
+    ref, _ = _attention_ref(q2, B, S, Hq, Hkv, hd, 1.0 / math.sqrt(hd))
+    ref.backward(g.float())
+    assert _rel_err(out, ref) < 2e-2
+    W = (Hq + 2 * Hkv) * hd
+    gq, gr = qkv.grad.view(-1, W), q2.grad.view(-1, W)
+    assert _rel_err(gq[:, : Hq * hd], gr[:, : Hq * hd]) < 3e-2          # dQ
+    assert _rel_err(gq[:, Hq * hd: (Hq + Hkv) * hd], gr[:, Hq * hd: (Hq + Hkv) * hd]) < 3e-2   # dK
+    assert _rel_err(gq[:, (Hq + Hkv) * hd:], gr[:, (Hq + Hkv) * hd:]) < 3e-2   # dV
+
+
+def test_swiglu_embedding_ce_adam():
+    from piper_b200 import ops
+    from piper_b200.ops import native
+
+    torch.manual_seed(6)
+    h = torch.randn(333, 2 * 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    a = ops.swiglu(h)
+    g = torch.randn_like(a)
+    a.backward(g)
+    hr = h.detach().float().requires_grad_(True)
+    ar = torch.nn.functional.silu(hr[:, :1024]) * hr[:, 1024:]
+    ar.backward(g.float())
+    assert _rel_err(a, ar) < 1e-2 and _rel_err(h.grad, hr.grad) < 1e-2
+
+    table = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    tok = torch.randint(0, 1000, (4, 77), device="cuda")
+    e = ops.embedding(tok, table)
+    ge = torch.randn_like(e)
+    e.backward(ge)
+    tr = table.detach().float().requires_grad_(True)
+    torch.nn.functional.embedding(tok, tr).backward(ge.float())
+    assert torch.equal(e, table.detach()[tok])
+    assert _rel_err(table.grad, tr.grad) < 1e-2
+
+    V = 5000
+    logits = (torch.randn(257, V, device="cuda", dtype=torch.bfloat16) * 3).requires_grad_(True)
+    labels = torch.randint(0, V, (257,), device="cuda")
+    labels[5] = -100
+    loss = ops.cross_entropy(logits, labels)
+    loss.backward()
+    lr = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lr, labels)
+    ref.backward()
+    assert abs(loss.item() - ref.item()) < 1e-3 * max(1.0, abs(ref.item()))
+    assert _rel_err(logits.grad, lr.grad) < 2e-2
+
+    n = 100_003
+    master = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    grad = torch.randn(n, device="cuda")
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    pr = master.clone().requires_grad_(True)
+    opt = torch.optim.Adam([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    for step in (1, 2):
+        native.lib().adam_flat(master, m, v, grad, p16, 1e-2, 0.9, 0.95, 1e-8, 0.0, step, 1.0)
+        pr.grad = grad.clone()
+        opt.step()
+    assert _rel_err(master, pr.detach()) < 1e-5
+    assert _rel_err(p16, pr.detach()) < 1e-2

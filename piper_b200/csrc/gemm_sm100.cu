@@ -261,6 +261,13 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
   EncodeFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
+  // The driver entry point needs a current context on the calling thread;
+  // autograd's backward threads have only used the runtime API lazily.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    cudaFree(nullptr);
+    ctx_bound = true;
+  }
   const cuuint64_t dims[2] = {inner, outer};
   const cuuint64_t strides[1] = {row_stride_bytes};
   const cuuint32_t box[2] = {box_inner, box_outer};

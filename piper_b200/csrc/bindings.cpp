@@ -227,6 +227,14 @@ void cast_f32_to_bf16(const Tensor& in, Tensor out, double scale) {
            "cast_f32_to_bf16");
 }
 
+void add_bf16(const Tensor& a, const Tensor& b, Tensor out) {
+  check_bf16(a, "a");
+  check_bf16(b, "b");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && out.is_contiguous() && a.numel() == b.numel(),
+              "add_bf16 expects contiguous tensors of equal size");
+  check_rc(piper::add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), cur_stream()), "add_bf16");
+}
+
 void accum_bf16_into_f32(const Tensor& g, Tensor acc) {
   check_bf16(g, "g");
   TORCH_CHECK(g.is_contiguous() && acc.is_contiguous() && g.numel() == acc.numel(), "accum shape mismatch");
@@ -280,6 +288,7 @@ TORCH_LIBRARY(piper_c, m) {
   m.def("adam_flat", &adam_flat);
   m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
   m.def("accum_bf16_into_f32", &accum_bf16_into_f32);
+  m.def("add_bf16", &add_bf16);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   register_moe_ops(m);

@@ -509,6 +509,20 @@ __global__ void accum_bf16_into_f32_kernel(const __nv_bfloat16* __restrict__ g, 
     acc[i] += __bfloat162float(g[i]);
 }
 
+// out = a + b over n bf16 elements (n % 8 == 0): the residual add at a stage boundary.
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, long long nvec) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float x[8], y[8];
+    unpack8(reinterpret_cast<const bf16x8*>(a)[i], x);
+    unpack8(reinterpret_cast<const bf16x8*>(b)[i], y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += y[j];
+    reinterpret_cast<bf16x8*>(out)[i] = pack8(x);
+  }
+}
+
 inline int grid_for(long long work, int threads, int max_blocks = 148 * 16) {
   long long b = (work + threads - 1) / threads;
   if (b > max_blocks) b = max_blocks;
@@ -670,6 +684,15 @@ int adam_flat(float* master, float* m, float* v, const float* grad, void* param_
 int cast_f32_to_bf16(const float* in, void* out, long long n, float scale, cudaStream_t st) {
   if (n == 0) return 0;
   cast_f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(in, static_cast<__nv_bfloat16*>(out), n, scale);
+  return PIPER_LAUNCH_OK();
+}
+
+int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t st) {
+  if (n % 8 != 0) return -1;
+  if (n == 0) return 0;
+  add_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(a),
+                                                       static_cast<const __nv_bfloat16*>(b),
+                                                       static_cast<__nv_bfloat16*>(out), n / 8);
   return PIPER_LAUNCH_OK();
 }
 

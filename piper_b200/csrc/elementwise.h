@@ -51,6 +51,7 @@ int adam_flat(float* master, float* m, float* v, const float* grad, void* param_
               float lr, float b1, float b2, float eps, float wd, int step, float grad_scale,
               cudaStream_t st);
 int cast_f32_to_bf16(const float* in, void* out, long long n, float scale, cudaStream_t st);
+int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t st);
 int accum_bf16_into_f32(const void* g, float* acc, long long n, cudaStream_t st);
 
 }  // namespace piper

@@ -8,6 +8,7 @@ from .core import (
     grad_sinks,
     linear,
     qk_rope,
+    residual_add,
     rmsnorm,
     rope_tables,
     swiglu,
@@ -15,6 +16,6 @@ from .core import (
 )
 
 __all__ = [
-    "native", "linear", "rmsnorm", "add_rmsnorm", "qk_rope", "rope_tables", "attention", "swiglu",
+    "native", "linear", "rmsnorm", "add_rmsnorm", "qk_rope", "residual_add", "rope_tables", "attention", "swiglu",
     "embedding", "cross_entropy", "grad_sinks", "wgrad_store",
 ]

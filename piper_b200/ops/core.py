@@ -81,10 +81,11 @@ class WgradStore:
     def drain(queue: list) -> list[tuple[Tensor, Tensor]]:
         """Run the queued GEMMs.  Returns (weight, dW) pairs for weights without a sink."""
         out = []
-        for x2, dy2, w in queue:
-            dw = _linear_wgrad(x2, dy2, w)
-            if dw is not None:
-                out.append((w, dw))
+        with torch.no_grad():
+            for x2, dy2, w in queue:
+                dw = _linear_wgrad(x2, dy2, w)
+                if dw is not None:
+                    out.append((w, dw))
         queue.clear()
         return out
 
@@ -174,7 +175,7 @@ def _linear_backward(ctx, dy):
     dw = None
     if ctx.needs_input_grad[1]:
         if wgrad_store.active is not None:
-            wgrad_store.active.append((x2, dy2, w))
+            wgrad_store.active.append((x2.detach(), dy2.detach(), w))
         else:
             dw = _linear_wgrad(x2, dy2, w)
     return dx, dw
@@ -305,6 +306,24 @@ def add_rmsnorm(x: Tensor, res: Tensor, w: Tensor, eps: float = 1e-6) -> tuple[T
     """Returns (rmsnorm(x + res) * w, x + res)."""
     y, h, _ = add_rmsnorm_fwd(x, res, w, eps)
     return y, h
+
+
+@torch.library.custom_op("piper::residual_add", mutates_args=())
+def residual_add(a: Tensor, b: Tensor) -> Tensor:
+    """a + b for two activations of the same shape (the residual add that is not fused into a norm)."""
+    if _is_native(a) and a.dtype == torch.bfloat16 and a.numel() % 8 == 0:
+        out = torch.empty_like(a, memory_format=torch.contiguous_format)
+        native.lib().add_bf16(a.contiguous(), b.contiguous(), out)
+        return out
+    return a + b
+
+
+@residual_add.register_fake
+def _(a, b):
+    return torch.empty_like(a)
+
+
+residual_add.register_autograd(lambda ctx, g: (g, g))
 
 
 # --------------------------------------------------------------------------

@@ -1,0 +1,706 @@
+"""The per-GPU executor host (``PiperActor``) and its DAG executor.
+
+One process owns one GPU and one ``PiperActor``.  The actor receives the
+per-device training DAG of its pipeline rank, materialises the parameters of
+every bucket it computes, and replays the DAG once per training step.  Task
+semantics follow the reference interpreter (``src/executors.py:571-1003``):
+
+========== ===============================================================
+FWD        detach the inputs, run the segment's GraphModule, keep outputs
+BWD        loss on the last segment, ``autograd.backward`` into the inputs
+BWD_I      same with weight-gradient GEMMs queued instead of executed
+BWD_W      drain that queue
+SEND/RECV  one message per tensor on the channel's communicator
+REDUCE     data-parallel gradient all-reduce (last microbatch of a bucket)
+RS / AG    ZeRO reduce-scatter into the fp32 shard / parameter all-gather
+A2A        expert-parallel token exchange (variable row counts)
+UPD        optimizer step of every bucket, gradient reset
+========== ===============================================================
+
+What differs by design: microbatches are real slices of the step's batch and
+the loss is the mean over the global batch; every cross-stream edge of the
+DAG, temporal ones included, is enforced by a CUDA event rather than by host
+issue order; pipeline receives land in buffers sized from the traced
+shapes; per-microbatch losses are returned to the caller.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+import torch
+import torch.distributed as dist
+import torch.fx as fx
+
+from ..compiler.dag import (A2A, ALL_GATHER, COMPUTE, DEFAULT_STREAM, ORDER_DUMMY, RECV, REDUCE, REDUCE_SCATTER, SEND,
+                            UPD, TrainingDAG, TrainingDAGNode)
+from ..compiler.ordering import serial_topological_order
+from ..ops import core as ops_core
+from ..ops import native
+from ..state import LOG_LEVEL, create_logger
+from .faults import FaultInjector
+from .layout import ProcessGroups, RankLayout
+from .storage import AdamConfig, ParamSlot, ParamStorage, init_tensor
+
+logger = create_logger("piper_actor", LOG_LEVEL)
+
+
+@dataclass
+class StageBucket:
+    """Everything needed to run one segment GraphModule: its placeholders and where their values come from."""
+    key: str
+    gm: fx.GraphModule
+    n_placeholders: int
+    input_pos: list                     # placeholder positions fed by runtime inputs, in order
+    slots: list                         # ParamSlot per parameter/buffer placeholder
+    storage: Optional[ParamStorage] = None
+    constants: dict = field(default_factory=dict)    # placeholder position -> non-trainable tensor
+    input_meta: list = field(default_factory=list)   # (shape, dtype) of the runtime inputs at trace time
+
+    def build_args(self, inputs: list) -> list:
+        args: list = [None] * self.n_placeholders
+        for pos, t in zip(self.input_pos, inputs):
+            args[pos] = t
+        for pos, t in self.constants.items():
+            args[pos] = t
+        if self.storage is not None:
+            if not self.storage.params_ready():
+                raise RuntimeError(f"bucket {self.key}: parameters are sharded and were not gathered before use")
+            for pos, t in self.storage.param_views.items():
+                args[pos] = t
+        missing = [i for i, a in enumerate(args) if a is None]
+        if missing:
+            raise RuntimeError(f"bucket {self.key}: placeholders {missing} have no value "
+                               "(parameters not gathered, or an input is missing)")
+        return args
+
+
+class _Streams:
+    """Logical stream name -> CUDA stream (or nothing on CPU)."""
+
+    def __init__(self, device: torch.device, names: list[str]) -> None:
+        self.cuda = device.type == "cuda"
+        self.streams: dict[str, Any] = {}
+        if self.cuda:
+            for n in names:
+                self.streams[n] = torch.cuda.current_stream(device) if n == DEFAULT_STREAM else torch.cuda.Stream(device)
+
+    def get(self, name: str):
+        return self.streams.get(name)
+
+    def use(self, name: str):
+        if not self.cuda:
+            return _NullCtx()
+        return torch.cuda.stream(self.streams[name])
+
+
+class _NullCtx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+class PiperActor:
+    """Owns the runtime state of one GPU: groups, streams, buckets, the DAG and its dispatch order."""
+
+    def __init__(self, layout: RankLayout, groups: Optional[ProcessGroups], device: torch.device,
+                 model_dtype: torch.dtype = torch.bfloat16, adam: Optional[AdamConfig] = None, seed: int = 0,
+                 no_nvtx: bool = False, baseline: Optional[str] = None) -> None:
+        self.layout = layout
+        self.groups = groups
+        self.device = device
+        self.model_dtype = model_dtype
+        self.adam = adam or AdamConfig()
+        self.seed = seed
+        self.no_nvtx = no_nvtx or device.type != "cuda"
+        self.baseline = baseline            # "nccl": issue collectives exactly as the reference does
+        self.dag: Optional[TrainingDAG] = None
+        self.order: list[str] = []
+        self.buckets: dict[str, StageBucket] = {}
+        self.const_attrs: dict[str, torch.Tensor] = {}
+        self.inputs: list = []
+        self.labels: Optional[torch.Tensor] = None
+        self.num_microbatches = 1
+        self.iteration = 0
+        self.faults = FaultInjector(layout.dp_rank)
+        self.streams: Optional[_Streams] = None
+        self.last_losses: list = []
+        self.node_times: dict = {}
+        self.profile_nodes = False
+        self._profiler = None
+        self.fused = None                   # parallel.fused.FusedCollectives when enabled
+        self._channel_streams: dict = {}
+        self.debug_keep_grads = False       # tests: keep a scaled copy of the gradients each step
+        self.last_grads: dict = {}
+
+    # ------------------------------------------------------------ loading
+    def load_const_attrs(self, attrs: dict) -> None:
+        for k, v in (attrs or {}).items():
+            self.const_attrs[k] = v.to(self.device) if isinstance(v, torch.Tensor) else v
+
+    def load_training_dag(self, dag: TrainingDAG, num_microbatches: int) -> None:
+        self.dag = dag
+        self.num_microbatches = num_microbatches
+        names = sorted({n.stream for n in dag.nodes.values()} | {DEFAULT_STREAM})
+        self.streams = _Streams(self.device, names)
+        modes = self._bucket_modes(dag)
+        for node in dag.nodes.values():
+            if node.node_kind == COMPUTE and node.compute_subkind == "FWD":
+                key = node.node_meta["bucket_key"]
+                if key not in self.buckets:
+                    self.buckets[key] = self._load_bucket(key, node, modes.get(key, "local"))
+        self.order = serial_topological_order(dag)
+        self._prune_redundant_grad_sync()
+
+    def _bucket_modes(self, dag: TrainingDAG) -> dict:
+        modes: dict[str, str] = {}
+        for n in dag.nodes.values():
+            k = n.node_meta.get("bucket_key")
+            if n.node_kind == ALL_GATHER:
+                modes[k] = "zero3"
+            elif n.node_kind == REDUCE_SCATTER and modes.get(k) != "zero3":
+                modes[k] = "zero2"
+            elif n.node_kind == REDUCE and k not in modes:
+                modes[k] = "allreduce"
+        return modes
+
+    def _load_bucket(self, key: str, node: TrainingDAGNode, mode: str) -> StageBucket:
+        m = node.node_meta
+        gm: fx.GraphModule = m["gm"]
+        _relocate_meta_devices(gm, self.device)
+        phs = [n for n in gm.graph.nodes if n.op == "placeholder"]
+        gargs = m["graphargs"]
+        fqns = m.get("param_fqns") or [None] * len(phs)
+        ep = m.get("ep_shard")
+        ep_degree, ep_index = 1, 0
+        if ep:
+            ranks = _my_ep_ranks(ep, self.layout.global_rank)
+            ep_degree, ep_index = len(ranks), ranks.index(self.layout.global_rank)
+        slots, constants = [], {}
+        for pos in m["param_idxs"]:
+            g = gargs[pos]
+            fqn = fqns[pos] if pos < len(fqns) and fqns[pos] else phs[pos].name
+            trainable = bool(getattr(g, "requires_grad", False)) and g.is_floating_point()
+            shape = tuple(g.shape)
+            slot = ParamSlot(pos=pos, fqn=fqn, shape=shape, dtype=g.dtype, requires_grad=trainable)
+            if ep and trainable and ep_degree > 1 and len(shape) >= 1 and shape[0] % ep_degree == 0:
+                slot.ep_sharded, slot.full_shape = True, shape
+                slot.ep_index, slot.ep_degree = ep_index, ep_degree
+                slot.shape = (shape[0] // ep_degree, *shape[1:])
+            if trainable:
+                slots.append(slot)
+            else:
+                constants[pos] = self._constant_for(fqn, phs[pos].name, g)
+        storage = None
+        if slots:
+            if mode != "local" and self.layout.dp_degree == 1:
+                mode = "local"
+            if ep and ep_degree > 1:
+                mode = "local"          # experts are partitioned, not replicated: no data-parallel sync
+            dtype = slots[0].dtype
+            storage = ParamStorage(key, slots, self.device, dtype, mode, self.layout.dp_rank, self.layout.dp_degree,
+                                   self.groups.dp_group if self.groups else None, self.adam, self.seed)
+        input_meta = [(tuple(gargs[p].shape), gargs[p].dtype) for p in m["input_idxs"]]
+        return StageBucket(key=key, gm=gm, n_placeholders=len(phs), input_pos=list(m["input_idxs"]), slots=slots,
+                           storage=storage, constants=constants, input_meta=input_meta)
+
+    def _constant_for(self, fqn: str, ph_name: str, meta_t: torch.Tensor) -> torch.Tensor:
+        """Buffers and other non-trainable placeholders: taken from const_attrs by name, else zeros."""
+        for k, v in self.const_attrs.items():
+            if fqn == k or fqn.endswith("." + k) or k in ph_name:
+                t = v.to(self.device)
+                if t.is_floating_point() and meta_t.is_floating_point() and t.dtype != meta_t.dtype and \
+                        meta_t.dtype != torch.float32:
+                    t = t.to(meta_t.dtype)
+                return t
+        return torch.zeros(meta_t.shape, dtype=meta_t.dtype, device=self.device)
+
+    def _prune_redundant_grad_sync(self) -> None:
+        """Plain all-reduce buckets sync once per step: only the last REDUCE of a bucket does work."""
+        last: dict[str, str] = {}
+        for uid in self.order:
+            n = self.dag.nodes[uid]
+            if n.node_kind == REDUCE:
+                last[n.node_meta.get("bucket_key")] = uid
+        for uid in self.order:
+            n = self.dag.nodes[uid]
+            if n.node_kind == REDUCE:
+                n.node_meta["noop"] = last[n.node_meta.get("bucket_key")] != uid
+
+    # -------------------------------------------------------------- data
+    def load_input(self, inputs: list) -> None:
+        self.inputs = [t.to(self.device, non_blocking=True) if isinstance(t, torch.Tensor) else t for t in inputs]
+
+    def load_labels(self, labels) -> None:
+        self.labels = labels.to(self.device, non_blocking=True) if isinstance(labels, torch.Tensor) else labels
+
+    def has_first_stage(self) -> bool:
+        """True when some forward node takes the model inputs (no upstream segment, receive or exchange)."""
+        for n in self.dag.nodes.values():
+            if n.node_kind != COMPUTE or n.compute_subkind != "FWD":
+                continue
+            ups = [self.dag.nodes[p] for p in self.dag.data_preds(n.uid)]
+            if not any(u.node_kind in (RECV, A2A) or (u.node_kind == COMPUTE and u.compute_subkind == "FWD")
+                       for u in ups):
+                return True
+        return False
+
+    def has_loss_stage(self) -> bool:
+        return any(n.node_meta.get("compute_loss") for n in self.dag.nodes.values())
+
+    # --------------------------------------------------------------- step
+    def run_dag(self, loss_fn: Callable) -> dict:
+        if self.device.type == "cuda" and not self.no_nvtx:
+            torch.cuda.nvtx.range_push(f"iter_{self.iteration}_rank_{self.layout.global_rank}")
+        try:
+            out = DagExecutor(self).run(loss_fn)
+        finally:
+            if self.device.type == "cuda" and not self.no_nvtx:
+                torch.cuda.nvtx.range_pop()
+        self.iteration += 1
+        return out
+
+    # ---------------------------------------------------- memory / profile
+    def reset_peak_memory(self) -> None:
+        if self.device.type == "cuda":
+            torch.cuda.reset_peak_memory_stats(self.device)
+
+    def get_and_reset_peak_memory_stats(self) -> tuple[int, int]:
+        peak = torch.cuda.max_memory_allocated(self.device) if self.device.type == "cuda" else 0
+        self.reset_peak_memory()
+        return self.layout.global_rank, int(peak)
+
+    def start_pytorch_profiler(self) -> None:
+        from torch.profiler import ProfilerActivity, profile
+        acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if self.device.type == "cuda" else [])
+        self._profiler = profile(activities=acts)
+        self._profiler.__enter__()
+        self.profile_nodes = True
+
+    def stop_pytorch_profiler(self, out_dir: str) -> str:
+        import os
+        self._profiler.__exit__(None, None, None)
+        os.makedirs(out_dir, exist_ok=True)
+        path = os.path.join(out_dir, f"dp{self.layout.dp_rank}_pp{self.layout.pp_rank}.json")
+        self._profiler.export_chrome_trace(path)
+        self._profiler, self.profile_nodes = None, False
+        return path
+
+    # ---------------------------------------------------------- parameters
+    def named_parameters(self) -> dict[str, torch.Tensor]:
+        """fqn -> full parameter tensor held by this rank (gathers ZeRO-3 shards)."""
+        out = {}
+        for b in self.buckets.values():
+            if b.storage is None or b.storage.numel == 0:
+                continue
+            flat = b.storage.full_param_tensor()
+            for s in b.storage.slots:
+                out[s.fqn] = flat[s.offset:s.offset + s.numel].view(s.shape)
+        return out
+
+    def named_grads(self) -> dict[str, torch.Tensor]:
+        out = {}
+        for b in self.buckets.values():
+            st = b.storage
+            if st is None or st.flat_grads is None:
+                continue
+            for s in st.slots:
+                out[s.fqn] = st.flat_grads[s.offset:s.offset + s.numel].view(s.shape)
+        return out
+
+
+def _my_ep_ranks(ep: dict, rank: int) -> list:
+    groups = ep.get("groups")
+    if groups:
+        for g in groups:
+            if rank in g:
+                return list(g)
+    return list(ep["devices"])
+
+
+def _relocate_meta_devices(gm: fx.GraphModule, device: torch.device) -> None:
+    """Graphs are traced on ``meta``; device literals baked into factory calls must point at the real device."""
+    changed = False
+    for n in gm.graph.nodes:
+        if n.op in ("call_function", "call_method") and "device" in n.kwargs:
+            d = n.kwargs["device"]
+            if (isinstance(d, torch.device) and d.type == "meta") or d == "meta":
+                kw = dict(n.kwargs)
+                kw["device"] = device
+                n.kwargs = kw
+                changed = True
+        new_args = tuple(device if (isinstance(a, torch.device) and a.type == "meta") else a for a in n.args)
+        if new_args != tuple(n.args):
+            n.args = new_args
+            changed = True
+    if changed:
+        gm.recompile()
+
+
+class DagExecutor:
+    """Replays the actor's dispatch order once: one training step."""
+
+    def __init__(self, actor: PiperActor) -> None:
+        self.a = actor
+        self.dag = actor.dag
+        self.cuda = actor.device.type == "cuda"
+        self.events: dict[str, Any] = {}
+        self.fwd_ctx: dict[str, tuple] = {}      # fwd uid -> (detached inputs, outputs)
+        self.outs: dict[str, Any] = {}           # producer uid -> tuple of tensors for data successors
+        self.pending: list = []                  # async send/recv work handles
+        self.wgrad_queues: dict[str, list] = {}
+        self.shape_ref: dict[str, list] = {}
+        self.losses: list = []
+
+    # ----------------------------------------------------------- helpers
+    def _mb(self, node: TrainingDAGNode) -> int:
+        v = node.tag.get("MB", 0)
+        return int(v) if v is not None else 0
+
+    def _microbatch(self, t, mb: int):
+        if not isinstance(t, torch.Tensor) or t.dim() == 0:
+            return t
+        n = self.a.num_microbatches
+        if t.shape[0] % n == 0 and t.shape[0] >= n:
+            per = t.shape[0] // n
+            return t[mb * per:(mb + 1) * per]
+        return t
+
+    def _stream(self, node: TrainingDAGNode):
+        """CUDA stream a node runs on.  Pipeline messages get one stream per channel, so a send that waits for
+        its peer never blocks a receive of another channel queued behind it."""
+        if node.node_kind in (SEND, RECV):
+            key = tuple(node.node_meta.get("channel") or ())
+            st = self.a._channel_streams.get(key)
+            if st is None:
+                st = self.a._channel_streams[key] = torch.cuda.Stream(self.a.device)
+            return st
+        return self.a.streams.get(node.stream)
+
+    def _wait_preds(self, node: TrainingDAGNode) -> None:
+        if not self.cuda:
+            return
+        s = self._stream(node)
+        p2p = node.node_kind in (SEND, RECV)
+        for e in self.dag.in_edges(node.uid):
+            p = e.src_uid
+            pn = self.dag.nodes[p]
+            if p not in self.events:
+                continue
+            # order between pipeline messages is host issue order only; an event wait on a send that is
+            # itself waiting for the peer could stall a receive the peer needs first
+            if p2p and pn.node_kind in (SEND, RECV) and e.dep_kind == "temporal":
+                continue
+            ev, ps = self.events[p]
+            if ps is not s:
+                s.wait_event(ev)
+
+    def _record(self, node: TrainingDAGNode) -> None:
+        if self.cuda:
+            s = self._stream(node)
+            ev = torch.cuda.Event()
+            ev.record(s)
+            self.events[node.uid] = (ev, s)
+
+    def _inputs_for(self, node: TrainingDAGNode) -> list:
+        """Runtime inputs of a forward node: outputs of the previous segment, a receive or an exchange buffer,
+        or (first segment) this microbatch's slice of the step's model inputs."""
+        for p in self.dag.data_preds(node.uid):
+            pn = self.dag.nodes[p]
+            if p in self.outs and (pn.node_kind in (RECV, A2A)
+                                   or (pn.node_kind == COMPUTE and pn.compute_subkind == "FWD")):
+                self._wait_work(p)
+                return list(self.outs[p])
+        return [self._microbatch(t, self._mb(node)) for t in self.a.inputs]
+
+    def _wait_work(self, uid: str) -> None:
+        for w in self._works.pop(uid, []):
+            w.wait()
+
+    # --------------------------------------------------------------- run
+    def run(self, loss_fn: Callable) -> dict:
+        a = self.a
+        self._works: dict[str, list] = {}
+        t0 = time.perf_counter()
+        if self.cuda:
+            # side streams must see the previous step's update before they touch parameters again
+            cur = a.streams.get(DEFAULT_STREAM)
+            for name, s in a.streams.streams.items():
+                if name != DEFAULT_STREAM:
+                    s.wait_stream(cur)
+            for s in a._channel_streams.values():
+                s.wait_stream(cur)
+        for uid in a.order:
+            node = self.dag.nodes[uid]
+            kind = node.node_kind
+            label = None
+            if self.cuda and (not a.no_nvtx or a.profile_nodes):
+                tags = ",".join(f"{k}={v}" for k, v in sorted(node.tag.items(), key=lambda kv: kv[0]) if v is not None)
+                label = f"{kind}:{tags}:uid{uid}"
+                if not a.no_nvtx:
+                    torch.cuda.nvtx.range_push(label)
+            rf = torch.profiler.record_function(label) if (a.profile_nodes and label) else _NullCtx()
+            with rf, (torch.cuda.stream(self._stream(node)) if self.cuda else _NullCtx()):
+                self._wait_preds(node)
+                if kind == COMPUTE:
+                    sub = node.compute_subkind
+                    if sub == "FWD":
+                        self._forward(node)
+                    elif sub == "BWD":
+                        a.faults.maybe_fire("bwd", a.iteration)
+                        self._backward(node, loss_fn, split=False)
+                    elif sub == "BWD_I":
+                        a.faults.maybe_fire("bwd", a.iteration)
+                        self._backward(node, loss_fn, split=True)
+                    elif sub == "BWD_W":
+                        self._backward_weight(node)
+                elif kind == SEND:
+                    self._send(node)
+                elif kind == RECV:
+                    self._recv(node)
+                elif kind == REDUCE:
+                    self._all_reduce(node)
+                elif kind == REDUCE_SCATTER:
+                    self._reduce_scatter(node)
+                elif kind == ALL_GATHER:
+                    self._all_gather(node)
+                elif kind == A2A:
+                    self._all_to_all(node)
+                elif kind == UPD:
+                    self._update(node)
+                self._record(node)
+            if label is not None and not a.no_nvtx:
+                torch.cuda.nvtx.range_pop()
+        for ws in self._works.values():
+            for w in ws:
+                w.wait()
+        for w in self.pending:
+            w.wait()
+        if self.cuda:
+            # later steps reuse buffers on the default stream: fence the side streams behind it
+            cur = a.streams.get(DEFAULT_STREAM)
+            for name, s in a.streams.streams.items():
+                if name != DEFAULT_STREAM:
+                    cur.wait_stream(s)
+            for s in a._channel_streams.values():
+                cur.wait_stream(s)
+        a.last_losses = self.losses
+        return {"losses": self.losses, "host_time_s": time.perf_counter() - t0}
+
+    # ------------------------------------------------------------ compute
+    def _forward(self, node: TrainingDAGNode) -> None:
+        a = self.a
+        bucket = a.buckets[node.node_meta["bucket_key"]]
+        raw = self._inputs_for(node)
+        ins = []
+        for t in raw:
+            if isinstance(t, torch.Tensor):
+                t = t.detach()
+                if t.is_floating_point():
+                    t.requires_grad_(True)
+            ins.append(t)
+        outs = bucket.gm(*bucket.build_args(ins))
+        outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
+        self.fwd_ctx[node.uid] = (ins, outs)
+        self.outs[node.uid] = outs
+        self.shape_ref[node.uid] = [(tuple(o.shape), o.dtype) for o in outs
+                                    if isinstance(o, torch.Tensor) and o.requires_grad]
+        if node.node_meta.get("zero_free_full_params_after") and bucket.storage is not None:
+            bucket.storage.free_params(a.streams.get(node.stream) if self.cuda else None)
+
+    def _output_grads(self, node: TrainingDAGNode) -> Optional[list]:
+        """Gradients w.r.t. this segment's outputs, produced by the downstream backward / recv / a2a node."""
+        for p in self.dag.data_preds(node.uid):
+            pn = self.dag.nodes[p]
+            if p not in self.outs:
+                continue
+            if pn.node_kind in (RECV, A2A) or (pn.node_kind == COMPUTE and pn.compute_subkind in ("BWD", "BWD_I")):
+                self._wait_work(p)
+                return list(self.outs[p])
+        return None
+
+    def _backward(self, node: TrainingDAGNode, loss_fn: Callable, split: bool) -> None:
+        a = self.a
+        fwd_uid = node.node_meta["fwd_uid"]
+        bucket = a.buckets[node.node_meta["bucket_key"]]
+        st = bucket.storage
+        if st is not None and node.node_meta.get("zero_alloc_full_grads_before"):
+            st.alloc_grads()
+        ins, outs = self.fwd_ctx.pop(fwd_uid)
+        self.outs.pop(fwd_uid, None)
+        if split:
+            ops_core.wgrad_store.begin()
+        try:
+            if node.node_meta.get("compute_loss"):
+                labels = self._microbatch(a.labels, self._mb(node))
+                loss = loss_fn(outs[0], labels)
+                self.losses.append(loss.detach())
+                loss.backward()
+            else:
+                grads = self._output_grads(node)
+                if grads is None:
+                    raise RuntimeError(f"{node.uid}: no upstream gradient available")
+                diff_outs = [o for o in outs if isinstance(o, torch.Tensor) and o.requires_grad]
+                gs = [g for g in grads if g is not None]
+                if len(gs) != len(diff_outs):
+                    # position-wise pairing when the consumer reported a gradient slot per input
+                    pairs = [(o, g) for o, g in zip(outs, grads)
+                             if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]
+                    diff_outs, gs = [p[0] for p in pairs], [p[1] for p in pairs]
+                if diff_outs:
+                    torch.autograd.backward(diff_outs, gs)
+        finally:
+            if split:
+                self.wgrad_queues[node.uid] = ops_core.wgrad_store.end()
+        in_grads = tuple(t.grad if isinstance(t, torch.Tensor) and t.is_floating_point() else None for t in ins)
+        self.outs[node.uid] = in_grads
+        if st is not None and st.flat_grads is not None:
+            st.absorb_autograd_grads()
+        if not split and node.node_meta.get("zero_free_full_params_after") and st is not None:
+            st.free_params(a.streams.get(node.stream) if self.cuda else None)
+
+    def _backward_weight(self, node: TrainingDAGNode) -> None:
+        a = self.a
+        bucket = a.buckets[node.node_meta["bucket_key"]]
+        st = bucket.storage
+        bi_uid = next((p for p in self.dag.data_preds(node.uid)
+                       if self.dag.nodes[p].node_kind == COMPUTE and self.dag.nodes[p].compute_subkind == "BWD_I"), None)
+        queue = self.wgrad_queues.pop(bi_uid, []) if bi_uid else []
+        if st is not None and node.node_meta.get("zero_alloc_full_grads_before"):
+            st.alloc_grads()
+        for w, dw in ops_core.WgradStore.drain(queue):
+            sink = ops_core.grad_sinks.get(w)
+            if sink is not None:
+                sink.add_(dw.to(torch.float32))
+            elif w.grad is None:
+                w.grad = dw
+            else:
+                w.grad.add_(dw)
+        if st is not None and st.flat_grads is not None:
+            st.absorb_autograd_grads()
+        if node.node_meta.get("zero_free_full_params_after") and st is not None:
+            st.free_params(a.streams.get(node.stream) if self.cuda else None)
+
+    # ---------------------------------------------------- communication
+    def _channel(self, node: TrainingDAGNode):
+        key = node.node_meta.get("channel")
+        if key is None:
+            raise RuntimeError(f"{node.uid}: pipeline channel was not assigned")
+        return self.a.groups.channel(tuple(key))
+
+    def _send(self, node: TrainingDAGNode) -> None:
+        a = self.a
+        src = node.node_meta["from_uid"]
+        vals = self.outs.get(src)
+        if vals is None:
+            raise RuntimeError(f"{node.uid}: nothing to send from {src}")
+        peer = a.layout.peer_rank(node.node_meta["peer_pp_rank"])
+        group, tag = self._channel(node)
+        for t in vals:
+            if not isinstance(t, torch.Tensor):
+                continue
+            t = t.detach().contiguous()
+            w = dist.isend(t, dst=peer, group=group, tag=tag)
+            if self.cuda:
+                w.wait()                 # stream-level wait only; the host does not block
+            else:
+                self.pending.append(_Hold(w, t))
+
+    def _recv(self, node: TrainingDAGNode) -> None:
+        a = self.a
+        m = node.node_meta
+        peer = a.layout.peer_rank(m["peer_pp_rank"])
+        group, tag = self._channel(node)
+        consumer = self.dag.nodes[m["to_uid"]]
+        if consumer.compute_subkind == "FWD":
+            metas = a.buckets[consumer.node_meta["bucket_key"]].input_meta
+        else:
+            metas = self.shape_ref[consumer.node_meta["fwd_uid"]]
+        bufs, works = [], []
+        for shape, dtype in metas:
+            buf = torch.empty(shape, dtype=dtype, device=a.device)
+            w = dist.irecv(buf, src=peer, group=group, tag=tag)
+            if self.cuda:
+                w.wait()
+            else:
+                works.append(w)
+            bufs.append(buf)
+        self.outs[node.uid] = tuple(bufs)
+        self._works[node.uid] = works
+
+    def _storage_of(self, node: TrainingDAGNode) -> Optional[ParamStorage]:
+        b = self.a.buckets.get(node.node_meta.get("bucket_key"))
+        return None if b is None else b.storage
+
+    def _all_reduce(self, node: TrainingDAGNode) -> None:
+        if node.node_meta.get("noop"):
+            return
+        st = self._storage_of(node)
+        if st is None or st.mode != "allreduce":
+            return
+        a = self.a
+        if a.fused is not None and a.fused.supports(st):
+            a.fused.reduce_scatter_adam(st, 1.0 / (a.num_microbatches * a.layout.dp_degree))
+            st.fused_stepped = True
+        else:
+            st.all_reduce_grads(per_tensor=(a.baseline == "nccl"))
+
+    def _reduce_scatter(self, node: TrainingDAGNode) -> None:
+        st = self._storage_of(node)
+        if st is None or st.mode not in ("zero2", "zero3"):
+            return
+        if not st.release_grads():
+            if node.node_meta.get("zero_free_full_params_after"):
+                st.free_params(self.a.streams.get(node.stream) if self.cuda else None)
+            return
+        st.reduce_scatter_grads()
+        if st.mode == "zero3":
+            st.free_grads(self.a.streams.get(node.stream) if self.cuda else None)
+        else:
+            st.flat_grads.zero_()
+        if node.node_meta.get("zero_free_full_params_after"):
+            st.free_params(self.a.streams.get(node.stream) if self.cuda else None)
+
+    def _all_gather(self, node: TrainingDAGNode) -> None:
+        st = self._storage_of(node)
+        if st is not None and st.mode == "zero3":
+            st.all_gather_params()
+
+    def _all_to_all(self, node: TrainingDAGNode) -> None:
+        from ..parallel.expert import exchange_tokens
+        m = node.node_meta
+        src = self.dag.data_preds(node.uid)[0]
+        vals = list(self.outs[src])
+        self._wait_work(src)
+        self.outs[node.uid] = exchange_tokens(self, node, vals)
+
+    def _update(self, node: TrainingDAGNode) -> None:
+        a = self.a
+        scale = 1.0 / (a.num_microbatches * a.layout.dp_degree)
+        if a.debug_keep_grads:
+            a.last_grads = {}
+        for b in a.buckets.values():
+            st = b.storage
+            if st is None or st.numel == 0:
+                continue
+            if a.debug_keep_grads:
+                a.last_grads.update(st.snapshot_grads(scale))
+            if getattr(st, "fused_stepped", False):
+                st.fused_stepped = False
+                continue
+            ep_scale = scale
+            st.step(ep_scale)
+
+
+class _Hold:
+    """Keeps a tensor alive until its asynchronous send has completed."""
+
+    def __init__(self, work, tensor) -> None:
+        self.work, self.tensor = work, tensor
+
+    def wait(self) -> None:
+        self.work.wait()
+        self.tensor = None

@@ -1,0 +1,136 @@
+"""End-to-end equivalence on CPU/gloo: every parallel layout reproduces the single-process loss and gradients."""
+import pytest
+import torch
+
+from tests.dist_utils import run_ranks
+
+SEQ = 128
+
+
+def _data(cfg, batch, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    tok = torch.randint(0, cfg.vocab_size, (batch, SEQ + 1), generator=g)
+    return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+
+
+def _reference(batch, steps=1, lr=1e-3):
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.nn import cross_entropy_loss
+    from piper_b200.runtime.storage import materialize_module
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    x, y = _data(cfg, batch)
+    m = Transformer(cfg, SEQ, 1)
+    m.load_const_attrs()
+    materialize_module(m)
+    opt = torch.optim.Adam(m.parameters(), lr=lr)
+    out = {}
+    for step in range(steps):
+        opt.zero_grad()
+        loss = cross_entropy_loss(m(x), y)
+        loss.backward()
+        if step == 0:
+            out["loss"] = float(loss.detach())
+            out["grads"] = {n: p.grad.clone() for n, p in m.named_parameters()}
+        opt.step()
+    out["params"] = {n: p.detach().clone() for n, p in m.named_parameters()}
+    return out
+
+
+def _worker(rank, world, schedule, num_stages, global_batch, dp, steps):
+    from piper_b200 import piper_exec_dag, piper_setup
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.nn import cross_entropy_loss
+    from piper_b200.runtime.layout import make_layout
+    from piper_b200.compiler.schedule import stage_device_map
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    x, y = _data(cfg, global_batch)
+    layout = make_layout(stage_device_map(schedule), rank, world)
+    per = global_batch // dp
+    xs, ys = x[layout.dp_rank * per:(layout.dp_rank + 1) * per], y[layout.dp_rank * per:(layout.dp_rank + 1) * per]
+    actor = piper_setup(Transformer, (cfg, SEQ, num_stages), optim_fn=torch.optim.Adam, example_inputs=[xs],
+                        example_outputs=ys, model_dtype=torch.float32, const_attrs=Transformer.const_attrs(cfg, SEQ),
+                        schedule_directives=schedule, device="cpu")
+    actor.debug_keep_grads = True
+    first = None
+    for _ in range(steps):
+        losses = piper_exec_dag(cross_entropy_loss)
+        if first is None:
+            first = ([float(l) for l in losses], dict(actor.last_grads))
+    params = {k: v.detach().clone() for k, v in actor.named_parameters().items()}
+    return {"losses": first[0], "grads": first[1], "params": params, "dp_rank": layout.dp_rank}
+
+
+def _check(results, ref, dp, atol=1e-5, check_params=False):
+    losses = [l for r in results for l in r["losses"]]
+    assert losses, "no rank reported a loss"
+    assert abs(sum(losses) / len(losses) - ref["loss"]) < atol
+    seen = set()
+    for r in results:
+        for k, g in r["grads"].items():
+            if isinstance(g, tuple):      # ZeRO shard: (offset inside the parameter, flat values)
+                off, vals = g
+                want = ref["grads"][k].reshape(-1)[off:off + vals.numel()]
+                assert torch.allclose(vals, want, atol=atol), k
+            else:
+                assert torch.allclose(g, ref["grads"][k], atol=atol), k
+            seen.add(k)
+    assert seen == set(ref["grads"]), sorted(set(ref["grads"]) - seen)
+    if check_params:
+        for r in results:
+            for k, p in r["params"].items():
+                # Adam turns a 1e-8 gradient difference on a near-zero gradient into an lr-sized step
+                # difference, so the bound is per-step lr for the maximum and tight for the mean
+                d = (p - ref["params"][k]).abs()
+                assert d.max() <= 2.5e-3 and d.mean() < 2e-5, (k, float(d.max()), float(d.mean()))
+
+
+def _sched(places, mbs, extra=(), order=()):
+    s = [{"op": "place", "filter": {"PP": i}, "devices": d, "stream": "pp_stream"} for i, d in enumerate(places)]
+    s += list(extra)
+    s.append({"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": mbs})
+    s += list(order)
+    return s
+
+
+def test_pp2_1f1b_matches_single_process(tmp_path):
+    """Two annotate('PP') regions of two layers on two ranks, 1F1B over 4 microbatches of a batch of 8."""
+    from piper_b200.compiler.builders import build_1f1b_schedule
+
+    sched = _sched([[0], [1]], 4, order=build_1f1b_schedule(2, 4))
+    res = run_ranks(2, _worker, (sched, 2, 8, 1, 1), tmp_path)
+    _check(res, _reference(8), dp=1)
+
+
+def test_dp2_allreduce_matches_single_process(tmp_path):
+    sched = _sched([[0, 1]], 2, extra=[{"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1],
+                                        "reduce_stream": "dp_stream"}])
+    res = run_ranks(2, _worker, (sched, 1, 8, 2, 2), tmp_path)
+    _check(res, _reference(8, steps=2), dp=2, check_params=True)
+
+
+@pytest.mark.parametrize("flags", [{"shard_grads": True}, {"shard_grads": True, "shard_params": True}])
+def test_dp2_zero_matches_single_process(tmp_path, flags):
+    sched = _sched([[0, 1]], 2, extra=[{"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1],
+                                        "gather_stream": "dp_stream", "reduce_stream": "dp_stream", **flags}])
+    res = run_ranks(2, _worker, (sched, 1, 8, 2, 2), tmp_path)
+    _check(res, _reference(8, steps=2), dp=2, check_params=True)
+
+
+def test_pp2_dp2_zerobubble_matches_single_process(tmp_path):
+    from piper_b200.compiler.builders import build_zerobubble_schedule
+
+    extra = [{"op": "replicate", "filter": {"PP": 0}, "devices": [0, 2], "reduce_stream": "dp_stream"},
+             {"op": "replicate", "filter": {"PP": 1}, "devices": [1, 3], "reduce_stream": "dp_stream"}]
+    sched = _sched([[0, 2], [1, 3]], 2, extra=extra, order=build_zerobubble_schedule(2, 2))
+    res = run_ranks(4, _worker, (sched, 2, 8, 2, 1), tmp_path)
+    _check(res, _reference(8), dp=2)
+
+
+def test_interleaved_v_placement_four_stages_on_two_ranks(tmp_path):
+    from piper_b200.compiler.builders import build_dualpipev_schedule
+
+    sched = _sched([[0], [1], [1], [0]], 4, order=build_dualpipev_schedule(2, 4))
+    res = run_ranks(2, _worker, (sched, 4, 8, 1, 1), tmp_path)
+    _check(res, _reference(8), dp=1)

@@ -6,6 +6,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <torch/library.h>
 
+#include <atomic>
+
 #include "attention_sm100.h"
 #include "elementwise.h"
 #include "gemm_sm100.h"
@@ -34,9 +36,15 @@ void check_bf16(const Tensor& t, const char* name) {
   TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
 }
 
-void check_rc(int rc, const char* what) {
+// Number of kernels of this library launched by this process (benchmarks report it).
+std::atomic<int64_t> g_kernel_launches{0};
+
+void check_rc(int rc, const char* what, int kernels = 1) {
   TORCH_CHECK(rc == 0, "piper_c::", what, " failed with code ", rc);
+  g_kernel_launches.fetch_add(kernels, std::memory_order_relaxed);
 }
+
+int64_t kernel_launch_count() { return g_kernel_launches.load(std::memory_order_relaxed); }
 
 const void* opt_ptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 float* opt_f32(const OptTensor& t) {
@@ -119,7 +127,7 @@ void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tenso
                               dx.data_ptr(), dw_partial.data_ptr<float>(), opt_f32(dw_f32),
                               dw_bf16.has_value() ? dw_bf16->data_ptr() : nullptr, accumulate ? 1 : 0, T,
                               static_cast<int>(D), cur_stream()),
-           "rmsnorm_bwd");
+           "rmsnorm_bwd", 2);
 }
 
 void qk_rope_fwd(const Tensor& qkv, Tensor out, const Tensor& cos, const Tensor& sin, const OptTensor& qw,
@@ -264,7 +272,7 @@ void attn_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, const Te
                            delta.data_ptr<float>(), dqkv.data_ptr(), static_cast<int>(B), static_cast<int>(S),
                            static_cast<int>(Hq), static_cast<int>(Hkv), static_cast<int>(hd),
                            static_cast<float>(scale), status.data_ptr<int>(), cur_stream()),
-           "attn_bwd");
+           "attn_bwd", 3);
 }
 
 }  // namespace
@@ -273,6 +281,7 @@ void attn_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, const Te
 #include "bindings_fused.inc"
 
 TORCH_LIBRARY(piper_c, m) {
+  m.def("kernel_launch_count", &kernel_launch_count);
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_num_partials", &rmsnorm_bwd_num_partials);

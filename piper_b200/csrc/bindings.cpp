@@ -7,6 +7,7 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <cmath>
 
 #include "attention_sm100.h"
 #include "elementwise.h"

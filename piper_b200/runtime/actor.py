@@ -211,11 +211,8 @@ class PiperActor:
         """Buffers and other non-trainable placeholders: taken from const_attrs by name, else zeros."""
         for k, v in self.const_attrs.items():
             if fqn == k or fqn.endswith("." + k) or k in ph_name:
-                t = v.to(self.device)
-                if t.is_floating_point() and meta_t.is_floating_point() and t.dtype != meta_t.dtype and \
-                        meta_t.dtype != torch.float32:
-                    t = t.to(meta_t.dtype)
-                return t
+                # the provided tensor keeps its dtype: rotary tables stay fp32 even when the module was cast to bf16
+                return v.to(self.device)
         return torch.zeros(meta_t.shape, dtype=meta_t.dtype, device=self.device)
 
     def _prune_redundant_grad_sync(self) -> None:

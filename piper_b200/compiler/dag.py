@@ -27,6 +27,7 @@ REDUCE_SCATTER = "REDUCE_SCATTER_COMM"
 A2A = "A2A_COMM"
 ORDER_DUMMY = "ORDER_DUMMY"
 DEFAULT_STREAM = "default_stream"
+STASH_EDGE = "__activations__"   # tensor_name of the forward -> own backward edge
 
 
 @dataclass(frozen=True)
@@ -305,6 +306,10 @@ def build_training_dag(segments: list) -> TrainingDAG:
         ))
     for a, b in zip(fwd_uids, fwd_uids[1:]):
         dag.connect(f"{b}.bwd", f"{a}.bwd", "data")
+    # a backward consumes the activations its forward stashed: a real dependency that also keeps the forward
+    # and backward halves of a pipeline rank in one connected component when no order directive links them
+    for f in fwd_uids:
+        dag.connect(f, f"{f}.bwd", "data", STASH_EDGE)
     if fwd_uids:
         last = max(fwd_uids, key=lambda u: (dag.nodes[u].node_meta["stage_id"], dag.nodes[u].node_meta["segment_id"]))
         dag.connect(last, f"{last}.bwd", "data")

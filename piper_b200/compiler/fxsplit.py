@@ -152,7 +152,8 @@ def _arg_nodes(x: Any, acc: Optional[list] = None) -> list:
     return acc
 
 
-def _boundary_info(crossing: list, consumers_next: set, produced_prev: set, from_tag: dict, to_tag: dict) -> dict:
+def _boundary_info(crossing: list, consumers_next: set, produced_prev: set, from_tag: dict, to_tag: dict,
+                   ends_in_next: Optional[set] = None) -> dict:
     """Which crossing value an expert-parallel exchange at this boundary moves.
 
     Preference: a floating-point tensor that the next segment's own compute consumes and that the
@@ -184,7 +185,12 @@ def _boundary_info(crossing: list, consumers_next: set, produced_prev: set, from
         return (isinstance(ex, torch.Tensor) and not ex.is_floating_point() and ex.dtype != torch.bool
                 and ex.dim() == 1 and (n in consumers_next or n in produced_prev))
 
-    return {"tensor_idx": idx, "counts_idx": pick(is_counts), "reshape_input": None, "reshape_output": None,
+    # the per-expert row counts of an exchange are consumed by the next segment only; an integer vector that
+    # merely passes through (and is needed again later) must not be rewritten by the exchange
+    cidx = pick(lambda n: is_counts(n) and n in consumers_next and (ends_in_next is None or n in ends_in_next))
+    if cidx is None:
+        cidx = pick(lambda n: is_counts(n) and n in consumers_next)
+    return {"tensor_idx": idx, "counts_idx": cidx, "reshape_input": None, "reshape_output": None,
             "from_tag": from_tag, "to_tag": to_tag}
 
 
@@ -304,8 +310,9 @@ def split_gm_by_annotations(gm: fx.GraphModule) -> tuple[fx.GraphModule, list[An
             out_names = [n.name for n in crossing[s + 1]]
             nxt_body = [n for n in compute if seg_of[n] == s + 1]
             consumers_next = {d for n in nxt_body for d in n.all_input_nodes}
+            ends_next = {n for n in crossing[s + 1] if last_use[n] == s + 1}
             after = _boundary_info(crossing[s + 1], consumers_next, set(body), _tag(seg_stacks[s]),
-                                   _tag(seg_stacks[s + 1]))
+                                   _tag(seg_stacks[s + 1]), ends_next)
         g.lint()
         seg_gm = fx.GraphModule(gm, g)
         tag = _tag(seg_stacks[s])

@@ -19,7 +19,7 @@ from __future__ import annotations
 
 from typing import Any
 
-from .dag import ALL_GATHER, COMPUTE, REDUCE, REDUCE_SCATTER, TrainingDAG
+from .dag import ALL_GATHER, COMPUTE, REDUCE, REDUCE_SCATTER, STASH_EDGE, TrainingDAG
 from .ordering import serial_topological_order
 
 
@@ -54,6 +54,8 @@ def _chains(dag: TrainingDAG, candidates: list[str], order: list[str]) -> list[l
 
         for u in uids:
             for e in dag.out_edges(u):
+                if e.tensor_name == STASH_EDGE:
+                    continue    # forward -> own backward: not adjacency in time, parameters are released in between
                 if e.dst_uid in members:
                     ra, rb = find(u), find(e.dst_uid)
                     if ra != rb:

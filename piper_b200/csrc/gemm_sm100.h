@@ -36,6 +36,35 @@ struct GemmArgs {
 // CUresult of a failed tensor-map encode.
 int gemm_bf16_launch(const GemmArgs& args, int num_sms, cudaStream_t stream);
 
+enum : int {
+  kGroupedFwd = 0,     // Y[rows, N]  = X[rows, K] * W[e]^T
+  kGroupedDgrad = 1,   // dX[rows, K] = dY[rows, N] * W[e]
+  kGroupedWgrad = 2,   // dW[e][N, K] (+)= dY[rows_e]^T * X[rows_e]   (fp32 output)
+};
+
+// Grouped GEMMs of the expert MLP.  Rows of x / dy / out are grouped: group g
+// owns rows [g_start[g], g_start[g] + g_len[g]), g_len a multiple of 128 with
+// zero padding rows, and uses expert g % experts of w [experts, N, K].
+// g_start / g_len live on the device.  rows_capacity is the row count of the
+// row buffers.  out is bf16 [rows_capacity, N] (fwd), bf16 [rows_capacity, K]
+// (dgrad) or fp32 [experts, N, K] (wgrad; accumulate selects += or =).
+struct GroupedGemmArgs {
+  int mode;
+  const void* x;        // [rows_capacity, K]   (fwd, wgrad)
+  const void* dy;       // [rows_capacity, N]   (dgrad, wgrad)
+  const void* w;        // [experts, N, K]      (fwd, dgrad)
+  void* out;
+  const int* g_start;
+  const int* g_len;
+  int num_groups, experts;
+  int N, K;
+  long long rows_capacity;
+  int accumulate;
+  int* status;
+};
+
+int grouped_gemm_launch(const GroupedGemmArgs& args, int num_sms, cudaStream_t stream);
+
 // Encodes a 2-D bf16 tensor map with 128-byte swizzle.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);

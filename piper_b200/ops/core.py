@@ -64,7 +64,7 @@ grad_sinks = GradSinks()
 
 
 class WgradStore:
-    """Queue of deferred weight-gradient GEMMs (x, dy, weight) of one backward-input pass."""
+    """Queue of deferred weight-gradient GEMMs of one backward-input pass: (thunk returning dW or None, weight)."""
 
     def __init__(self) -> None:
         self.active: Optional[list] = None
@@ -82,8 +82,8 @@ class WgradStore:
         """Run the queued GEMMs.  Returns (weight, dW) pairs for weights without a sink."""
         out = []
         with torch.no_grad():
-            for x2, dy2, w in queue:
-                dw = _linear_wgrad(x2, dy2, w)
+            for fn, w in queue:
+                dw = fn()
                 if dw is not None:
                     out.append((w, dw))
         queue.clear()
@@ -175,7 +175,8 @@ def _linear_backward(ctx, dy):
     dw = None
     if ctx.needs_input_grad[1]:
         if wgrad_store.active is not None:
-            wgrad_store.active.append((x2.detach(), dy2.detach(), w))
+            xd, dyd = x2.detach(), dy2.detach()
+            wgrad_store.active.append((lambda: _linear_wgrad(xd, dyd, w), w))
         else:
             dw = _linear_wgrad(x2, dy2, w)
     return dx, dw

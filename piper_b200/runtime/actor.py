@@ -133,6 +133,7 @@ class PiperActor:
         self._profiler = None
         self.fused = None                   # parallel.fused.FusedCollectives when enabled
         self._channel_streams: dict = {}
+        self._ep_splits: dict = {}          # (MB, PP, EP) -> split sizes shared by a layer's four token exchanges
         self.debug_keep_grads = False       # tests: keep a scaled copy of the gradients each step
         self.last_grads: dict = {}
 
@@ -504,20 +505,24 @@ class DagExecutor:
         self.fwd_ctx[node.uid] = (ins, outs)
         self.outs[node.uid] = outs
         self.shape_ref[node.uid] = [(tuple(o.shape), o.dtype) for o in outs
-                                    if isinstance(o, torch.Tensor) and o.requires_grad]
+                                    if isinstance(o, torch.Tensor) and o.is_floating_point()]
         if node.node_meta.get("zero_free_full_params_after") and bucket.storage is not None:
             bucket.storage.free_params(a.streams.get(node.stream) if self.cuda else None)
 
-    def _output_grads(self, node: TrainingDAGNode) -> Optional[list]:
-        """Gradients w.r.t. this segment's outputs, produced by the downstream backward / recv / a2a node."""
+    def _output_grads(self, node: TrainingDAGNode):
+        """Gradients w.r.t. this segment's outputs from the downstream backward / receive / exchange node.
+
+        Returns ``(grads, compact)``; ``compact`` is True for a pipeline receive, whose list has one entry per
+        floating-point output instead of one per output.
+        """
         for p in self.dag.data_preds(node.uid):
             pn = self.dag.nodes[p]
             if p not in self.outs:
                 continue
             if pn.node_kind in (RECV, A2A) or (pn.node_kind == COMPUTE and pn.compute_subkind in ("BWD", "BWD_I")):
                 self._wait_work(p)
-                return list(self.outs[p])
-        return None
+                return list(self.outs[p]), pn.node_kind == RECV
+        return None, False
 
     def _backward(self, node: TrainingDAGNode, loss_fn: Callable, split: bool) -> None:
         a = self.a
@@ -537,22 +542,25 @@ class DagExecutor:
                 self.losses.append(loss.detach())
                 loss.backward()
             else:
-                grads = self._output_grads(node)
+                grads, compact = self._output_grads(node)
                 if grads is None:
                     raise RuntimeError(f"{node.uid}: no upstream gradient available")
-                diff_outs = [o for o in outs if isinstance(o, torch.Tensor) and o.requires_grad]
-                gs = [g for g in grads if g is not None]
-                if len(gs) != len(diff_outs):
-                    # position-wise pairing when the consumer reported a gradient slot per input
-                    pairs = [(o, g) for o, g in zip(outs, grads)
-                             if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]
-                    diff_outs, gs = [p[0] for p in pairs], [p[1] for p in pairs]
-                if diff_outs:
-                    torch.autograd.backward(diff_outs, gs)
+                if compact:
+                    # received over a pipeline channel: one gradient per floating-point output, in order
+                    it = iter(grads)
+                    grads = [next(it) if isinstance(o, torch.Tensor) and o.is_floating_point() else None
+                             for o in outs]
+                pairs = [(o, g) for o, g in zip(outs, grads)
+                         if isinstance(o, torch.Tensor) and o.requires_grad and g is not None]
+                if pairs:
+                    torch.autograd.backward([p[0] for p in pairs], [p[1] for p in pairs])
         finally:
             if split:
                 self.wgrad_queues[node.uid] = ops_core.wgrad_store.end()
-        in_grads = tuple(t.grad if isinstance(t, torch.Tensor) and t.is_floating_point() else None for t in ins)
+        # one slot per input; a floating-point input that received no gradient reports zeros, so that both ends
+        # of a pipeline channel agree on "one message per floating-point tensor"
+        in_grads = tuple((t.grad if t.grad is not None else torch.zeros_like(t))
+                         if isinstance(t, torch.Tensor) and t.is_floating_point() else None for t in ins)
         self.outs[node.uid] = in_grads
         if st is not None and st.flat_grads is not None:
             st.absorb_autograd_grads()

@@ -134,3 +134,56 @@ def test_interleaved_v_placement_four_stages_on_two_ranks(tmp_path):
     sched = _sched([[0], [1], [1], [0]], 4, order=build_dualpipev_schedule(2, 4))
     res = run_ranks(2, _worker, (sched, 4, 8, 1, 1), tmp_path)
     _check(res, _reference(8), dp=1)
+
+
+def _moe_reference(batch):
+    from piper_b200.models.qwen3 import QWEN3_CONFIGS, PiperQwen3Model
+    from piper_b200.nn import cross_entropy_loss
+    from piper_b200.runtime.storage import materialize_module
+
+    cfg = QWEN3_CONFIGS["9M"]
+    x, y = _data(cfg, batch)
+    m = PiperQwen3Model(cfg, 1, SEQ)
+    m.load_const_attrs()
+    materialize_module(m)
+    loss = cross_entropy_loss(m(x), y)
+    loss.backward()
+    return {"loss": float(loss.detach()), "grads": {n: p.grad.clone() for n, p in m.named_parameters()}}
+
+
+def _moe_worker(rank, world, schedule, num_stages, global_batch, dp):
+    from piper_b200 import piper_exec_dag, piper_setup
+    from piper_b200.compiler.schedule import stage_device_map
+    from piper_b200.models.qwen3 import QWEN3_CONFIGS, PiperQwen3Model
+    from piper_b200.nn import cross_entropy_loss
+    from piper_b200.runtime.layout import make_layout
+
+    cfg = QWEN3_CONFIGS["9M"]
+    x, y = _data(cfg, global_batch)
+    layout = make_layout(stage_device_map(schedule), rank, world)
+    per = global_batch // dp
+    xs, ys = x[layout.dp_rank * per:(layout.dp_rank + 1) * per], y[layout.dp_rank * per:(layout.dp_rank + 1) * per]
+    actor = piper_setup(PiperQwen3Model, (cfg, num_stages, SEQ), optim_fn=torch.optim.Adam, example_inputs=[xs],
+                        example_outputs=ys, model_dtype=torch.float32,
+                        const_attrs=PiperQwen3Model.const_attrs(cfg, SEQ), schedule_directives=schedule, device="cpu")
+    actor.debug_keep_grads = True
+    losses = [float(l) for l in piper_exec_dag(cross_entropy_loss)]
+    return {"losses": losses, "grads": dict(actor.last_grads), "dp_rank": layout.dp_rank}
+
+
+def test_expert_parallel_dp2_ep2_matches_single_process(tmp_path):
+    """True expert parallelism: experts partitioned over two ranks, rows exchanged with per-expert counts."""
+    extra = [{"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1], "reduce_stream": "dp_stream"},
+             {"op": "shard", "filter": {"PP": 0, "EP": "*"}, "devices": [0, 1], "stream": "ep_stream"}]
+    sched = _sched([[0, 1]], 2, extra=extra)
+    res = run_ranks(2, _moe_worker, (sched, 1, 4, 2), tmp_path)
+    ref = _moe_reference(4)
+    losses = [l for r in res for l in r["losses"]]
+    assert abs(sum(losses) / len(losses) - ref["loss"]) < 1e-5
+    for r in res:
+        for k, g in r["grads"].items():
+            want = ref["grads"][k]
+            if g.shape != want.shape:            # expert weights: this rank holds its slice of the experts
+                per = want.shape[0] // 2
+                want = want[r["dp_rank"] * per:(r["dp_rank"] + 1) * per]
+            assert torch.allclose(g, want, atol=2e-5), (k, float((g - want).abs().max()))

@@ -565,6 +565,7 @@ def bucket_matched_fwd_nodes(dag: TrainingDAG, filters: list[dict], bucket_size_
             bgm, b_in, b_par, b_args = bucket[:4]
             b_fqns = bucket[4] if len(bucket) > 4 else []
             fu = f"{f_uid}.bucket{i}"
+            bkey = f"{m.get('bucket_key', f_uid)}.bucket{i}"     # shared by all microbatch copies
             f_chain.append(fu)
             b_chain.append(f"{fu}.bwd")
             dag.add_node(TrainingDAGNode(fu, COMPUTE, "FWD", with_pass_tag(fn.tag, "F"),
@@ -574,10 +575,10 @@ def bucket_matched_fwd_nodes(dag: TrainingDAG, filters: list[dict], bucket_size_
                 "param_fqns": list(b_fqns) if b_fqns else [],
                 "input_names": [x.name for x in bgm.graph.nodes if x.op == "placeholder"], "output_names": [],
                 "a2a_boundary_after": m.get("a2a_boundary_after") if i == len(buckets) - 1 else None,
-                "bucket_idx": i, "num_buckets": len(buckets), "bucket_key": fu, "parent_uid": f_uid}))
+                "bucket_idx": i, "num_buckets": len(buckets), "bucket_key": bkey, "parent_uid": f_uid}))
             dag.add_node(TrainingDAGNode(f"{fu}.bwd", COMPUTE, "BWD", with_pass_tag(fn.tag, "B"),
                                          None if bn.device is None else list(bn.device), bn.stream, {
-                "fwd_uid": fu, "bucket_idx": i, "num_buckets": len(buckets), "bucket_key": fu,
+                "fwd_uid": fu, "bucket_idx": i, "num_buckets": len(buckets), "bucket_key": bkey,
                 "compute_loss": bool(bn.node_meta.get("compute_loss", False)) and i == len(buckets) - 1}))
         del fqns
         first_f, last_f, first_b, last_b = f_chain[0], f_chain[-1], b_chain[-1], b_chain[0]

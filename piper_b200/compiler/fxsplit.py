@@ -92,6 +92,8 @@ def source_fqn(node: fx.Node) -> Optional[str]:
     ``L['self']._modules['layers']._modules['0']._parameters['weight']``; falls back to decoding the
     placeholder name (``l_self_modules_layers_modules_0_parameters_weight_``).
     """
+    if node.meta.get("piper_fqn"):
+        return node.meta["piper_fqn"]
     src = getattr(node, "_dynamo_source", None)
     name = getattr(src, "name", None) if src is not None else None
     if callable(name):
@@ -194,7 +196,10 @@ def _boundary_info(crossing: list, consumers_next: set, produced_prev: set, from
             "from_tag": from_tag, "to_tag": to_tag}
 
 
-def split_gm_by_annotations(gm: fx.GraphModule) -> tuple[fx.GraphModule, list[AnnotationSegment]]:
+def split_gm_by_annotations(gm: fx.GraphModule, runtime_input_names: Optional[set] = None
+                            ) -> tuple[fx.GraphModule, list[AnnotationSegment]]:
+    """Split ``gm`` into annotated segments.  ``runtime_input_names`` overrides the classification of
+    placeholders (used when a stage graph, whose inputs are crossing values, is split again into buckets)."""
     nodes = list(gm.graph.nodes)
     compute = [n for n in nodes if n.op not in _NON_COMPUTE]
     stacks = {n: annotation_stack(n) for n in compute}
@@ -213,7 +218,10 @@ def split_gm_by_annotations(gm: fx.GraphModule) -> tuple[fx.GraphModule, list[An
         seg_of[n] = len(seg_stacks) - 1
     n_segs = len(seg_stacks)
 
-    runtime_ph = [n for n in nodes if n.op == "placeholder" and placeholder_is_runtime_input(n)]
+    if runtime_input_names is not None:
+        runtime_ph = [n for n in nodes if n.op == "placeholder" and n.name in runtime_input_names]
+    else:
+        runtime_ph = [n for n in nodes if n.op == "placeholder" and placeholder_is_runtime_input(n)]
     param_ph = {n for n in nodes if n.op == "placeholder" and n not in set(runtime_ph)}
     output_node = next((n for n in nodes if n.op == "output"), None)
 
@@ -261,7 +269,10 @@ def split_gm_by_annotations(gm: fx.GraphModule) -> tuple[fx.GraphModule, list[An
             else:
                 param_idxs.append(pos)
                 graphargs.append(_meta_like(ex, requires_grad=rg, as_parameter=isinstance(ex, torch.nn.Parameter) or rg))
-                fqns.append(source_fqn(n))
+                fqn = source_fqn(n)
+                fqns.append(fqn)
+                if fqn:
+                    ph.meta["piper_fqn"] = fqn
 
         if s == 0:
             for n in runtime_ph:

@@ -238,6 +238,8 @@ def piper_exec_dag(loss_fn: Callable, log_stats: bool = False, step_timeout: Opt
             raise box["err"]
         results.append(box["out"])
     step_time = time.perf_counter() - t0
+    from .runtime.launcher import heartbeat
+    heartbeat(next(iter(actors.values())).iteration)
     if log_stats:
         msg = [f"step_time={step_time:.3f}s"]
         if piper_metadata.tokens_per_step:

@@ -18,16 +18,18 @@ def test_router_forward_backward(T, E, k):
     logits = (torch.randn(T, E, device="cuda") * 2).to(torch.bfloat16).requires_grad_(True)
     w, idx, counts = M.moe_route(logits, k, True)
     lr = logits.detach().cpu().float().requires_grad_(True)
-    wr, idxr, countsr = M.moe_route(lr, k, True)
-    assert torch.equal(idx.cpu().sort(-1).values, idxr.sort(-1).values)
-    assert torch.equal(counts.cpu(), countsr)
-    assert _rel(w.sort(-1).values, wr.sort(-1).values) < 1e-3
+    p = torch.softmax(lr, dim=-1)
+    # bf16 logits tie often and tie-breaking is implementation-defined: check the selection by value
+    kth = torch.topk(p, k, dim=-1).values[:, -1:]
+    sel = torch.gather(p, 1, idx.cpu().long())
+    assert (sel >= kth - 1e-6).all()
+    assert all(len(set(r)) == k for r in idx.cpu().tolist())
+    assert torch.equal(counts.cpu(), torch.bincount(idx.cpu().reshape(-1).long(), minlength=E).to(torch.int32))
+    wr = sel / sel.sum(-1, keepdim=True)
+    assert _rel(w, wr) < 1e-3
     g = torch.randn(T, k, device="cuda")
-    # align the gradient with each implementation's own ordering of the selected experts
     (w * g).sum().backward()
-    gref = torch.zeros(T, E)
-    gref.scatter_(1, idx.cpu().long(), g.cpu())
-    (wr * torch.gather(gref, 1, idxr.long())).sum().backward()
+    (wr * g.cpu()).sum().backward()
     assert _rel(logits.grad, lr.grad) < 2e-2
     native.check_status()
 

@@ -1,0 +1,193 @@
+"""Harness, coordinator / health monitoring, checkpointing, visualisation and trace merging on CPU."""
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+SEQ = 64
+
+
+# ----------------------------------------------------------------- harness
+def test_harness_dry_run_writes_schedule_and_prints_command(tmp_path):
+    cmd = [sys.executable, str(ROOT / "examples" / "test_harness.py"), "--test-file", str(ROOT / "examples" / "test_qwen.py"),
+           "--base-schedule", str(ROOT / "examples" / "base-schedules" / "pp4_dp2_ep2_v_placement.json"),
+           "--schedule", "dualpipev", "--ranks", "2", "--mbs", "4", "--dry-run", "--viz", "--out-root", str(tmp_path),
+           "--model", "9M"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-2000:]
+    gen = [l for l in out.stdout.splitlines() if l.startswith("generated_schedule=")][0].split("=", 1)[1]
+    sched = json.load(open(gen))
+    assert Path(gen).name == "dualpipev_pp2_mbs4.json"
+    assert sum(1 for d in sched if d["op"] == "order") == 2
+    assert [d for d in sched if d["op"] == "split"][0]["num_microbatches"] == 4
+    assert any(l.startswith("schedule_viz=") for l in out.stdout.splitlines())
+    # a generated order that crosses the placement is rejected
+    bad = cmd.copy()
+    bad[bad.index(str(ROOT / "examples" / "base-schedules" / "pp4_dp2_ep2_v_placement.json"))] = \
+        str(ROOT / "examples" / "base-schedules" / "pp4_dp2_ep2_interleaved.json")
+    out2 = subprocess.run(bad, capture_output=True, text=True, timeout=300, cwd=str(ROOT))
+    assert out2.returncode != 0 and "not compatible with the base placement" in out2.stderr
+
+
+# ------------------------------------------------------- health monitoring
+def _train_fn(args, pg):
+    """Two data-parallel CPU ranks training a tiny Llama; honours PIPER_FAULT."""
+    import torch
+    from piper_b200 import piper_exec_dag, piper_setup
+    from piper_b200.models.llama3 import LlamaConfig, Transformer
+    from piper_b200.nn import cross_entropy_loss
+
+    cfg = LlamaConfig(dim=64, n_layers=2, n_heads=2, n_kv_heads=2, vocab_size=128, ffn_hidden=128, max_seq_len=SEQ)
+    x = torch.randint(0, 128, (4, SEQ))
+    sched = [{"op": "place", "filter": {"PP": 0}, "devices": [0, 1]},
+             {"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1], "reduce_stream": "dp_stream"},
+             {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 2}]
+    piper_setup(Transformer, (cfg, SEQ, 1), optim_fn=torch.optim.Adam, example_inputs=[x], example_outputs=x,
+                model_dtype=torch.float32, const_attrs=Transformer.const_attrs(cfg, SEQ), schedule_directives=sched,
+                device="cpu")
+    losses = []
+    for _ in range(args["steps"]):
+        losses.append(float(piper_exec_dag(cross_entropy_loss, step_timeout=args.get("step_timeout"))[0]))
+    return losses
+
+
+def test_fault_injection_fails_fast_and_names_the_rank(monkeypatch):
+    from piper_b200.runtime.launcher import Coordinator, JobFailed
+
+    monkeypatch.setenv("PIPER_FAULT", "bwd:1:1")
+    coord = Coordinator(world_size=2)
+    t0 = time.time()
+    with pytest.raises(JobFailed) as ei:
+        coord.run_program(_train_fn, {"steps": 50}, timeout=240)
+    assert 1 in ei.value.result.failures and "PIPER_FAULT fired" in ei.value.result.failures[1]
+    assert time.time() - t0 < 200      # the healthy rank was stopped, not left waiting in a collective
+
+
+def test_healthy_job_returns_results_and_heartbeats():
+    from piper_b200.runtime.launcher import Coordinator
+
+    job = Coordinator(world_size=2, hang_timeout=120).run_program(_train_fn, {"steps": 2}, timeout=240)
+    assert job.ok and all(len(r) == 2 for r in job.results) and not job.hung
+    assert job.results[0][1] < job.results[0][0] + 0.5
+
+
+def test_sleeping_rank_is_reported_as_hung(monkeypatch):
+    from piper_b200.runtime.launcher import Coordinator
+
+    monkeypatch.setenv("PIPER_FAULT", "bwd:1:0:sleep:60")
+    coord = Coordinator(world_size=2, hang_timeout=8, kill_on_hang=True)
+    job = coord.run_program(_train_fn, {"steps": 3, "step_timeout": 2.0}, timeout=240, raise_on_failure=False)
+    assert not job.ok and job.hung, job
+
+
+def test_fault_spec_parsing():
+    from piper_b200.runtime.faults import FaultInjector, InjectedFault, parse_fault_spec
+
+    s = parse_fault_spec("bwd:3:1:sleep:2.5")
+    assert (s.point, s.iteration, s.dp_rank, s.action, s.seconds) == ("bwd", 3, 1, "sleep", 2.5)
+    assert parse_fault_spec("") is None
+    with pytest.raises(ValueError):
+        parse_fault_spec("fwd:1:0")
+    inj = FaultInjector(1, parse_fault_spec("bwd:2:1"))
+    inj.maybe_fire("bwd", 1)
+    with pytest.raises(InjectedFault):
+        inj.maybe_fire("bwd", 2)
+    inj.maybe_fire("bwd", 2)        # latched: fires once
+
+
+# ------------------------------------------------------------- checkpoint
+def _ckpt_worker(rank, world, schedule, dp, ckpt_dir, mode):
+    from piper_b200 import piper_exec_dag, piper_setup
+    from piper_b200.compiler.schedule import stage_device_map
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.nn import cross_entropy_loss
+    from piper_b200.runtime.checkpoint import load_checkpoint, save_checkpoint
+    from piper_b200.runtime.layout import make_layout
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, cfg.vocab_size, (4, 129), generator=g)
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    lay = make_layout(stage_device_map(schedule), rank, world)
+    per = 4 // dp
+    xs, ys = x[lay.dp_rank * per:(lay.dp_rank + 1) * per], y[lay.dp_rank * per:(lay.dp_rank + 1) * per]
+    actor = piper_setup(Transformer, (cfg, 128, len(stage_device_map(schedule))), optim_fn=torch.optim.Adam,
+                        example_inputs=[xs], example_outputs=ys, model_dtype=torch.float32,
+                        const_attrs=Transformer.const_attrs(cfg, 128), schedule_directives=schedule, device="cpu")
+    out = []
+    if mode == "save":
+        for _ in range(2):
+            out.append(sum(float(v) for v in piper_exec_dag(cross_entropy_loss)))
+        save_checkpoint(actor, ckpt_dir, step=2, schedule=schedule)
+        out.append(sum(float(v) for v in piper_exec_dag(cross_entropy_loss)))     # step 3 of the original run
+    else:
+        assert load_checkpoint(actor, ckpt_dir) == 2
+        out.append(sum(float(v) for v in piper_exec_dag(cross_entropy_loss)))     # step 3 after resume
+    return out
+
+
+def test_checkpoint_resume_under_a_different_layout(tmp_path):
+    """Save from DP2 with ZeRO-3, resume on PP2: the third step's loss is the same."""
+    from tests.dist_utils import run_ranks
+    from piper_b200.compiler.builders import build_1f1b_schedule
+    from piper_b200.runtime.checkpoint import consolidate
+
+    ck = str(tmp_path / "ckpt")
+    zero3 = [{"op": "place", "filter": {"PP": 0}, "devices": [0, 1]},
+             {"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1], "gather_stream": "dp_stream",
+              "reduce_stream": "dp_stream", "shard_grads": True, "shard_params": True},
+             {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 2}]
+    (tmp_path / "a").mkdir()
+    saved = run_ranks(2, _ckpt_worker, (zero3, 2, ck, "save"), tmp_path / "a")
+    full = consolidate(ck)
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    model = Transformer(LLAMA_CONFIGS["tiny"], 128, 1)
+    missing, unexpected = model.load_state_dict(full["model"], strict=False)
+    assert not unexpected and all("rope" in m for m in missing)
+    assert set(full["optimizer"]["state"]) == set(full["model"]) and full["step"] == 2
+    pp2 = [{"op": "place", "filter": {"PP": 0}, "devices": [0], "stream": "pp_stream"},
+           {"op": "place", "filter": {"PP": 1}, "devices": [1], "stream": "pp_stream"},
+           {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 4}, *build_1f1b_schedule(2, 4)]
+    (tmp_path / "b").mkdir()
+    resumed = run_ranks(2, _ckpt_worker, (pp2, 1, ck, "load"), tmp_path / "b")
+    step3_saved = (saved[0][2] + saved[1][2]) / 4          # 2 ranks x 2 microbatch losses
+    step3_resumed = sum(r[0] for r in resumed if r) / 4     # 4 microbatch losses on the last stage
+    assert abs(step3_saved - step3_resumed) < 2e-4, (step3_saved, step3_resumed)
+
+
+# ------------------------------------------------------------ viz / traces
+def test_viz_outputs_and_trace_relabel(tmp_path):
+    from piper_b200.compiler.builders import build_dualpipev_schedule
+    from piper_b200.compiler.dag import TrainingDAG, TrainingDAGNode
+    from piper_b200.compiler.viz import (compute_columns, print_training_dag_order, render_training_dag,
+                                         visualize_order_directives)
+    from piper_b200.runtime.profiler import relabel_gpu_events
+
+    order = build_dualpipev_schedule(2, 4)
+    path = visualize_order_directives(order, tmp_path / "grid.png")
+    text = open(path if path.endswith(".dot") else str(tmp_path / "grid.dot")).read()
+    assert "F0.3<BR/>B3.1" in text and "rank 1" in text
+    cols = compute_columns([d["filters"] for d in order])
+    assert all(c == sorted(c) for c in cols) and cols[1][0] > cols[0][0]      # stage 1 starts after stage 0
+    dag = TrainingDAG()
+    for u in ("a", "b"):
+        dag.add_node(TrainingDAGNode(u, "COMPUTE", "FWD", {"PP": 0, "PASS": "F"}, [0], "default_stream", {}))
+    dag.connect("a", "b", "data")
+    out = render_training_dag(dag, str(tmp_path / "training_dag_pp0"))
+    assert os.path.exists(out) and '"a" -> "b"' in open(str(tmp_path / "training_dag_pp0.dot")).read()
+    lines = print_training_dag_order(dag, label="pp0", rank=0, out_dir=str(tmp_path))
+    assert "FWD:PASS=F,PP=0:uida" in lines[1] and (tmp_path / "training_dag_order_rank0").exists()
+    events = [
+        {"ph": "X", "cat": "user_annotation", "name": "FWD:MB=0,PP=0:uids0.seg0", "ts": 100, "dur": 50, "tid": 1},
+        {"ph": "X", "cat": "cuda_runtime", "name": "cudaLaunchKernel", "ts": 110, "dur": 2, "tid": 1, "args": {"External id": 7}},
+        {"ph": "X", "cat": "kernel", "name": "gemm_kernel", "ts": 300, "dur": 20, "args": {"External id": 7}},
+        {"ph": "X", "cat": "kernel", "name": "other", "ts": 400, "dur": 20, "args": {"External id": 9}},
+    ]
+    assert relabel_gpu_events(events) == 1
+    assert events[2]["name"] == "FWD:MB=0,PP=0:uids0.seg0::gemm_kernel" and events[3]["name"] == "other"

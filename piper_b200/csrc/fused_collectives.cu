@@ -134,6 +134,154 @@ f1_kernel(const float* const* __restrict__ peer_grads, __nv_bfloat16* const* __r
     lg[i] = z;
 }
 
+// ===================================================================== F3
+// Expert-parallel dispatch and combine over peer memory.
+//
+// Every rank owns a receive buffer of ep regions (one per source rank, `cap`
+// rows each).  A token's row is written straight into the region that the
+// owner of its expert reserves for this source - the permutation into
+// expert order and the all-to-all are one pass of peer stores, with the
+// per-expert row counts and a "region complete" flag sent the same way.  The
+// owner then runs its grouped GEMMs over the regions (the group table is
+// built on the device from the received counts), publishes "outputs ready",
+// and the token's rank gathers its k expert outputs with peer loads while
+// applying the router weights: combine all-to-all and weighted sum in one
+// kernel.  No host synchronisation anywhere in the exchange.
+
+// seg_off[e]: first row of expert e inside the region this rank fills on the
+// owner of e (padded prefix over that owner's experts).  Also publishes this
+// rank's counts into every owner's metadata block.
+__global__ void ep_prepare_kernel(const int* __restrict__ counts, int* __restrict__ seg_off,
+                                  int* const* __restrict__ peer_meta, int my_rank, int ep, int experts_local) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  for (int d = 0; d < ep; ++d) {
+    int run = 0;
+    for (int l = 0; l < experts_local; ++l) {
+      const int e = d * experts_local + l;
+      seg_off[e] = run;
+      run += (counts[e] + 127) / 128 * 128;
+      peer_meta[d][my_rank * experts_local + l] = counts[e];
+    }
+  }
+}
+
+__global__ void ep_dispatch_push_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
+                                        const int* __restrict__ counts, const int* __restrict__ seg_off,
+                                        int* __restrict__ cursor, int* __restrict__ pos,
+                                        __nv_bfloat16* const* __restrict__ peer_recv,
+                                        uint64_t* const* __restrict__ peer_flags, unsigned int* cta_counter,
+                                        int my_rank, int ep, int experts_local, long long T, int D, int k, int cap,
+                                        unsigned long long epoch) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long w0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  for (long long t = w0; t < T; t += warps) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + t * D);
+    for (int j = 0; j < k; ++j) {
+      int d = 0, row = 0;
+      if (lane == 0) {
+        const int e = idx[t * k + j];
+        d = e / experts_local;
+        row = my_rank * cap + seg_off[e] + atomicAdd(cursor + e, 1);
+        pos[t * k + j] = d * (ep * cap) + row;
+      }
+      d = __shfl_sync(0xffffffffu, d, 0);
+      row = __shfl_sync(0xffffffffu, row, 0);
+      uint4* dst = reinterpret_cast<uint4*>(peer_recv[d] + static_cast<long long>(row) * D);
+      for (int i = lane; i < D / 8; i += 32) dst[i] = src[i];
+    }
+  }
+  // zero the padding rows of every segment this rank owns in the peers' regions
+  const int E = ep * experts_local;
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (int e = blockIdx.x; e < E; e += gridDim.x) {
+    const int d = e / experts_local;
+    const int first = my_rank * cap + seg_off[e] + counts[e];
+    const int last = my_rank * cap + seg_off[e] + (counts[e] + 127) / 128 * 128;
+    uint4* base = reinterpret_cast<uint4*>(peer_recv[d] + static_cast<long long>(first) * D);
+    const long long nvec = static_cast<long long>(last - first) * (D / 8);
+    for (long long i = threadIdx.x; i < nvec; i += blockDim.x) base[i] = z;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *cta_counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < ep; ++p) st_release_sys(peer_flags[p] + my_rank, epoch);
+    }
+  }
+}
+
+// Waits for every source's "region complete" flag, then builds the group
+// table of the regions: group (src, l) starts at src*cap + padded prefix.
+__global__ void ep_wait_table_kernel(const uint64_t* __restrict__ flags, const int* __restrict__ meta,
+                                     int* __restrict__ g_start, int* __restrict__ g_len, int* __restrict__ counts_out,
+                                     int ep, int experts_local, int cap, unsigned long long epoch,
+                                     unsigned long long timeout_ns, int* status) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (!wait_flags(flags, ep, epoch, timeout_ns, status)) return;
+  for (int s = 0; s < ep; ++s) {
+    int run = s * cap;
+    for (int l = 0; l < experts_local; ++l) {
+      const int g = s * experts_local + l;
+      const int c = meta[g];
+      const int len = (c + 127) / 128 * 128;
+      g_start[g] = run;
+      g_len[g] = len;
+      counts_out[g] = c;
+      run += len;
+    }
+  }
+}
+
+__global__ void ep_signal_kernel(uint64_t* const* __restrict__ peer_flags, int slot0, int my_rank, int ep,
+                                 unsigned long long epoch) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  __threadfence_system();
+  for (int p = 0; p < ep; ++p) st_release_sys(peer_flags[p] + slot0 + my_rank, epoch);
+}
+
+// out[t] = sum_j weights[t, j] * peer_out[owner(t, j)][row(t, j)].
+__global__ void ep_combine_pull_kernel(const __nv_bfloat16* const* __restrict__ peer_out, const int* __restrict__ pos,
+                                       const float* __restrict__ weights, __nv_bfloat16* __restrict__ out,
+                                       const uint64_t* __restrict__ out_flags, long long T, int D, int k, int ep,
+                                       int cap, unsigned long long epoch, unsigned long long timeout_ns,
+                                       int* status) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = wait_flags(out_flags, ep, epoch, timeout_ns, status) ? 1 : 0;
+  __syncthreads();
+  if (!ok_s) return;
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long region = static_cast<long long>(ep) * cap;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    for (int i = lane; i < D / 8; i += 32) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int j = 0; j < k; ++j) {
+        const int p = pos[t * k + j];
+        const int d = static_cast<int>(p / region);
+        const long long row = p % region;
+        const float w = weights[t * k + j];
+        const uint4 q = reinterpret_cast<const uint4*>(peer_out[d] + row * D)[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float2 f = __bfloat1622float2(h[c]);
+          acc[2 * c] += w * f.x;
+          acc[2 * c + 1] += w * f.y;
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) oh[c] = __floats2bfloat162_rn(acc[2 * c], acc[2 * c + 1]);
+      reinterpret_cast<uint4*>(out + t * D)[i] = o;
+    }
+  }
+}
+
 }  // namespace
 
 int f1_rs_adam_ag(const float* const* peer_grads, void* const* peer_params, uint64_t* const* peer_flags,
@@ -145,6 +293,46 @@ int f1_rs_adam_ag(const float* const* peer_grads, void* const* peer_params, uint
   f1_kernel<<<num_ctas, F1_THREADS, 0, st>>>(peer_grads, reinterpret_cast<__nv_bfloat16* const*>(peer_params),
                                             peer_flags, master, m, v, my_rank, dp, shard_numel, epoch, h,
                                             cta_counter, status, timeout_ns);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+}  // namespace piper
+
+namespace piper {
+
+int ep_dispatch_push(const void* x, const int* idx, const int* counts, int* seg_off, int* cursor, int* pos,
+                     void* const* peer_recv, int* const* peer_meta, uint64_t* const* peer_flags,
+                     unsigned int* cta_counter, int my_rank, int ep, int experts_local, long long T, int D, int k,
+                     int cap, unsigned long long epoch, int num_ctas, cudaStream_t st) {
+  if (D % 8 != 0 || ep < 1 || experts_local < 1) return -1;
+  ep_prepare_kernel<<<1, 32, 0, st>>>(counts, seg_off, peer_meta, my_rank, ep, experts_local);
+  ep_dispatch_push_kernel<<<num_ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), idx, counts, seg_off, cursor,
+                                                    pos, reinterpret_cast<__nv_bfloat16* const*>(peer_recv),
+                                                    peer_flags, cta_counter, my_rank, ep, experts_local, T, D, k, cap,
+                                                    epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int ep_wait_table(const uint64_t* flags, const int* meta, int* g_start, int* g_len, int* counts_out, int ep,
+                  int experts_local, int cap, unsigned long long epoch, unsigned long long timeout_ns, int* status,
+                  cudaStream_t st) {
+  ep_wait_table_kernel<<<1, 32, 0, st>>>(flags, meta, g_start, g_len, counts_out, ep, experts_local, cap, epoch,
+                                         timeout_ns, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int ep_signal(uint64_t* const* peer_flags, int slot0, int my_rank, int ep, unsigned long long epoch, cudaStream_t st) {
+  ep_signal_kernel<<<1, 32, 0, st>>>(peer_flags, slot0, my_rank, ep, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int ep_combine_pull(const void* const* peer_out, const int* pos, const float* weights, void* out,
+                    const uint64_t* out_flags, long long T, int D, int k, int ep, int cap, unsigned long long epoch,
+                    unsigned long long timeout_ns, int* status, int num_ctas, cudaStream_t st) {
+  if (D % 8 != 0) return -1;
+  ep_combine_pull_kernel<<<num_ctas, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16* const*>(peer_out), pos,
+                                                   weights, static_cast<__nv_bfloat16*>(out), out_flags, T, D, k, ep,
+                                                   cap, epoch, timeout_ns, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

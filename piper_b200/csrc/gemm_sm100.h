@@ -65,6 +65,24 @@ struct GroupedGemmArgs {
 
 int grouped_gemm_launch(const GroupedGemmArgs& args, int num_sms, cudaStream_t stream);
 
+constexpr int kMaxPeers = 8;
+
+// Y[M, N] = X[M, K] * W[N, K]^T with W sharded by rows: w_shards[p] points at
+// rank p's rows [p*rows_per_shard, (p+1)*rows_per_shard) (local or peer-mapped
+// memory, rows_per_shard a multiple of 64).  When w_full is not null the
+// gathered weight is also written there ([N, K], local memory).
+struct AgGemmArgs {
+  const void* x;
+  const void* w_shards[kMaxPeers];
+  void* w_full;
+  void* y;
+  int M, N, K;
+  int rows_per_shard, num_peers;
+  int* status;
+};
+
+int ag_gemm_launch(const AgGemmArgs& args, int num_sms, cudaStream_t stream);
+
 // Encodes a 2-D bf16 tensor map with 128-byte swizzle.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);

@@ -93,3 +93,105 @@ class FusedCollectives:
                                    lay.dp_degree, fb.epoch, a.lr, a.betas[0], a.betas[1], a.eps, a.weight_decay,
                                    st.step_count, grad_scale, fb.counter, native.status_tensor(st.device),
                                    self.timeout_s, self.num_ctas)
+
+
+# --------------------------------------------------------------------------------------------------
+# F2: ZeRO-3 all-gather fused into the consuming GEMM
+# --------------------------------------------------------------------------------------------------
+class ShardedWeight:
+    """A weight ``[N, K]`` sharded by rows over a group, each shard in symmetric memory.
+
+    ``linear(x)`` computes ``x @ W^T`` with one kernel that fetches every weight tile from the rank that owns
+    it (local HBM or a peer over NVLink) while the tensor cores work on the previous tile; with
+    ``keep_full=True`` the gathered weight is also written to a local ``[N, K]`` buffer for the backward GEMMs.
+    """
+
+    def __init__(self, full_weight: torch.Tensor, ranks: list, group, keep_full: bool = True) -> None:
+        N, K = full_weight.shape
+        dp = len(ranks)
+        me = list(ranks).index(dist.get_rank())
+        rows = (N + dp - 1) // dp
+        rows = (rows + 63) // 64 * 64
+        self.N, self.K, self.rows_per_shard, self.dp, self.index = N, K, rows, dp, me
+        self.buf = SymmetricBuffer.create(rows * K * 2, list(ranks), group)
+        self.shard = self.buf.view(torch.bfloat16, rows * K).view(rows, K)
+        lo, hi = me * rows, min((me + 1) * rows, N)
+        self.shard.zero_()
+        if hi > lo:
+            self.shard[:hi - lo].copy_(full_weight[lo:hi])
+        self.full = torch.empty((N, K), dtype=torch.bfloat16, device=full_weight.device) if keep_full else None
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def linear(self, x: torch.Tensor) -> torch.Tensor:
+        x2 = x.reshape(-1, self.K).contiguous()
+        y = torch.empty((x2.shape[0], self.N), dtype=torch.bfloat16, device=x.device)
+        native.lib().ag_gemm(x2, [int(p) for p in self.buf.ptrs], self.full, y, self.N, self.rows_per_shard,
+                             native.status_tensor(x.device))
+        return y.view(*x.shape[:-1], self.N)
+
+
+# --------------------------------------------------------------------------------------------------
+# F3: expert-parallel dispatch / combine over peer memory
+# --------------------------------------------------------------------------------------------------
+class FusedExpertExchange:
+    """Symmetric buffers and epochs of one expert-parallel group for the fused dispatch and combine kernels.
+
+    ``dispatch(x, idx, counts)`` scatters token rows into the expert owners' receive regions with peer stores
+    (permutation + all-to-all in one pass) and returns the owner-side view: the local receive buffer, its group
+    table and the flat count vector, valid once the kernel that waits for all sources has run on the stream.
+    ``combine(out_rows, pos, weights)`` publishes the local expert outputs and gathers each token's ``k`` outputs
+    from their owners with peer loads while applying the router weights.
+    """
+
+    def __init__(self, ranks: list, group, tokens: int, dim: int, experts: int, k: int, timeout_s: float = 30.0,
+                 num_ctas: int = 128) -> None:
+        from ..ops.moe import row_capacity
+        self.ranks, self.group = list(ranks), group
+        self.ep = len(ranks)
+        self.me = self.ranks.index(dist.get_rank())
+        self.T, self.D, self.E, self.k = tokens, dim, experts, k
+        self.El = experts // self.ep
+        self.cap = row_capacity(tokens, k, self.El)
+        self.timeout_s, self.num_ctas = timeout_s, num_ctas
+        rows = self.ep * self.cap
+        self.recv = SymmetricBuffer.create(rows * dim * 2, self.ranks, group)
+        self.out = SymmetricBuffer.create(rows * dim * 2, self.ranks, group)
+        self.meta = SymmetricBuffer.create(self.ep * self.El * 4, self.ranks, group)
+        self.flags = SymmetricBuffer.create(2 * self.ep * 8, self.ranks, group)
+        dev = self.recv.local.device
+        self.recv_rows = self.recv.view(torch.bfloat16, rows * dim).view(rows, dim)
+        self.out_rows = self.out.view(torch.bfloat16, rows * dim).view(rows, dim)
+        self.meta_local = self.meta.view(torch.int32, self.ep * self.El)
+        self.flags_local = self.flags.view(torch.int64, 2 * self.ep)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def dispatch(self, x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor):
+        lib = native.lib()
+        dev = x.device
+        self.epoch += 1
+        seg_off = torch.empty(self.E, dtype=torch.int32, device=dev)
+        cursor = torch.zeros(self.E, dtype=torch.int32, device=dev)
+        pos = torch.empty(x.shape[0] * self.k, dtype=torch.int32, device=dev)
+        lib.ep_dispatch_push(x.contiguous(), idx, counts, seg_off, cursor, pos, self.recv.peer_ptrs, self.meta.peer_ptrs,
+                             self.flags.peer_ptrs, self.counter, self.me, self.ep, self.cap, self.epoch, self.num_ctas)
+        G = self.ep * self.El
+        g_start = torch.empty(G, dtype=torch.int32, device=dev)
+        g_len = torch.empty(G, dtype=torch.int32, device=dev)
+        recv_counts = torch.empty(G, dtype=torch.int32, device=dev)
+        lib.ep_wait_table(self.flags_local, self.meta_local, g_start, g_len, recv_counts, self.ep, self.cap, self.epoch,
+                          self.timeout_s, native.status_tensor(dev))
+        return self.recv_rows, pos, g_start, g_len, recv_counts
+
+    def combine(self, pos: torch.Tensor, weights: torch.Tensor, tokens: int) -> torch.Tensor:
+        """Call after the expert outputs of this epoch have been written to ``self.out_rows``."""
+        lib = native.lib()
+        dev = weights.device
+        lib.ep_signal(self.flags.peer_ptrs, self.ep, self.me, self.ep, self.epoch)
+        out = torch.empty((tokens, self.D), dtype=torch.bfloat16, device=dev)
+        lib.ep_combine_pull(self.out.peer_ptrs, pos, weights.contiguous(), out, self.flags_local[self.ep:], self.ep,
+                            self.cap, self.epoch, self.timeout_s, native.status_tensor(dev), self.num_ctas)
+        return out

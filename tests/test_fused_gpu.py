@@ -85,3 +85,68 @@ def test_f1_matches_nccl_allreduce_adam_on_two_gpus(tmp_path):
         assert d.max() <= 8e-3 and d.mean() < 2e-4, (k, float(d.max()), float(d.mean()))
     assert abs(fused[0]["losses"][-1][0] - base[0]["losses"][-1][0]) < 5e-2
     assert fused[0]["losses"][-1][0] < fused[0]["losses"][0][0]
+
+
+def _f2_f3_worker(rank, world):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    from piper_b200.ops import moe as M, native
+    from piper_b200.parallel.fused import FusedExpertExchange, ShardedWeight
+    from piper_b200.runtime.layout import init_distributed
+
+    init_distributed("cuda")
+    dev = torch.device("cuda", rank)
+    ranks = list(range(world))
+    out = {}
+    # ---- F2: all-gather fused into the GEMM
+    g = torch.Generator(device="cpu").manual_seed(11)
+    N, K, T = 1000, 512, 384                  # N is not a multiple of the shard or tile size on purpose
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(dev)
+    sw = ShardedWeight(w, ranks, None, keep_full=True)
+    y = sw.linear(x)
+    torch.cuda.synchronize()
+    native.check_status()
+    ref = x.float() @ w.float().t()
+    out["f2_rel"] = ((y.float() - ref).norm() / ref.norm()).item()
+    out["f2_full_equal"] = bool(torch.equal(sw.full, w))
+    dist.barrier()
+    # ---- F3: dispatch push -> (identity expert x2) -> combine pull
+    Tt, D, E, k = 512, 256, 8, 2
+    g2 = torch.Generator(device="cpu").manual_seed(100 + rank)
+    xt = torch.randn(Tt, D, generator=g2).to(torch.bfloat16).to(dev)
+    logits = torch.randn(Tt, E, generator=g2).to(torch.bfloat16).to(dev)
+    weights, idx, counts = M.moe_route(logits, k, True)
+    ex = FusedExpertExchange(ranks, None, Tt, D, E, k, timeout_s=20.0)
+    for it in range(2):                        # two epochs: flags and buffers are reused
+        rows, pos, g_start, g_len, recv_counts = ex.dispatch(xt, idx, counts)
+        torch.cuda.synchronize()
+        native.check_status()
+        # received counts must equal what every source routed to this rank's experts
+        all_counts = [torch.empty_like(counts) for _ in ranks]
+        dist.all_gather(all_counts, counts)
+        El = E // world
+        want = torch.stack([c[rank * El:(rank + 1) * El] for c in all_counts]).reshape(-1)
+        out[f"f3_counts_ok_{it}"] = bool(torch.equal(recv_counts, want))
+        # "expert": double every valid row
+        ex.out_rows.copy_(rows * 2)
+        got = ex.combine(pos, weights, Tt)
+        torch.cuda.synchronize()
+        native.check_status()
+        refc = 2 * xt.float()
+        out[f"f3_rel_{it}"] = ((got.float() - refc).norm() / refc.norm()).item()
+        dist.barrier()
+    return out
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_f2_ag_gemm_and_f3_dispatch_combine_on_two_gpus(tmp_path):
+    from tests.dist_utils import run_ranks
+
+    res = run_ranks(2, _f2_f3_worker, (), tmp_path, timeout=600)
+    for r in res:
+        assert r["f2_rel"] < 1e-2 and r["f2_full_equal"], r
+        for it in range(2):
+            assert r[f"f3_counts_ok_{it}"], r
+            assert r[f"f3_rel_{it}"] < 1.5e-2, r

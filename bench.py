@@ -102,7 +102,7 @@ def run_ours(args) -> dict:
     import torch.distributed as dist
 
     from piper_b200 import piper_exec_dag, piper_setup
-    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer, balanced_stage_layers
     from piper_b200.nn import cross_entropy_loss
     from piper_b200.ops import native
 
@@ -115,7 +115,8 @@ def run_ours(args) -> dict:
     g = torch.Generator().manual_seed(1234 + rank)
     tok = torch.randint(0, cfg.vocab_size, (mbs, SEQ + 1), generator=g)
     x_host, y_host = tok[:, :-1].contiguous().pin_memory(), tok[:, 1:].contiguous().pin_memory()
-    actor = piper_setup(Transformer, (cfg, SEQ, pp), optim_fn=torch.optim.Adam, optim_kwargs={"lr": 1e-4},
+    split = balanced_stage_layers(cfg.n_layers, pp)
+    actor = piper_setup(Transformer, (cfg, SEQ, pp, split), optim_fn=torch.optim.Adam, optim_kwargs={"lr": 1e-4},
                         example_inputs=[x_host], example_outputs=y_host, model_dtype=torch.bfloat16,
                         const_attrs=Transformer.const_attrs(cfg, SEQ), schedule_directives=sched, device="cuda",
                         no_nvtx=True)
@@ -157,6 +158,13 @@ def run_ours(args) -> dict:
         return [float(v) for v in losses]      # device -> host read of the step's result
 
     ms_e2e, _, _, last_losses = timed(e2e_step)
+    host_ms = actor.last_host_time_s * 1e3
+    node_times = None
+    if os.environ.get("PIPER_BENCH_NODE_TIMES", "0") == "1":
+        actor.time_nodes = True
+        piper_exec_dag(cross_entropy_loss)
+        node_times = {k: {kk: round(vv, 2) for kk, vv in v.items()} for k, v in actor.node_times.items()}
+        actor.time_nodes = False
     native.check_status()
     tokens_per_step = GLOBAL_SEQS * SEQ
     value = tokens_per_step * args.steps / (ms_dev / 1e3)
@@ -170,13 +178,14 @@ def run_ours(args) -> dict:
         "higher_is_better": True, "scaling": "strong", "vs_baseline": value / PUBLISHED_TOKENS_PER_S,
         "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init N(0,0.02) weights",
         "config": {"model": f"llama3-{args.model}-shape", "global_batch": GLOBAL_SEQS, "seq_len": SEQ,
-                   "num_microbatches": mbs, "parallelism": f"pp{pp}dp{dp}", "schedule": "1f1b",
+                   "num_microbatches": mbs, "parallelism": f"pp{pp}dp{dp}", "schedule": "1f1b", "stage_layers": split,
                    "optimizer": "Adam, fp32 master + moments", "l2": "per-step working set >> 126 MB L2"},
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "impl": "piper_b200", "loss": (sum(last_losses) / len(last_losses)) if last_losses else None,
-        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
+        "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30, "host_ms_last_step": host_ms,
+        "node_times_rank0": node_times,
     }
 
 

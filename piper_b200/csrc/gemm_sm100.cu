@@ -21,6 +21,9 @@
 // All mbarrier waits are bounded; on expiry the kernel records a status code,
 // drains its TMA copies, frees TMEM and returns.
 #include "gemm_sm100.h"
+
+#include <cstdlib>
+
 #include "ptx.cuh"
 
 namespace piper {
@@ -45,13 +48,15 @@ struct Barriers {
   uint64_t acc_full[ACC_BUFS];
   uint64_t acc_empty[ACC_BUFS];
   uint32_t tmem_base;
+  int tile_ring[8];          // producer -> MMA warp: tile index of the n-th local tile (-1 = no more tiles)
+  int acc_tile[ACC_BUFS];    // MMA warp -> epilogue: tile index held by each accumulator (-1 = no more tiles)
 };
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             void* __restrict__ c_ptr, long long ldc, int M, int N, int K, int accumulate,
-            int* status) {
+            int* status, int* sched) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -70,7 +75,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       mbar_init(&bars->empty[s], 1);
     }
     for (int a = 0; a < ACC_BUFS; ++a) {
-      mbar_init(&bars->acc_full[a], 1);
+      mbar_init(&bars->acc_full[a], 2);    // tcgen05.commit + the MMA thread's own arrive (publishes acc_tile)
       mbar_init(&bars->acc_empty[a], 4);   // one arrive per epilogue warp
     }
     fence_mbar_init();
@@ -89,11 +94,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, n_local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      while (ok) {
+        // Tiles are handed out dynamically (one atomic per tile) so that a CTA that reaches the SM late,
+        // or shares the GPU with communication kernels, simply processes fewer tiles.
+        const int tile = sched != nullptr ? atomicAdd(&sched[0], 1)
+                                          : static_cast<int>(blockIdx.x + n_local * gridDim.x);
+        const bool none_left = tile >= num_tiles;
+        bars->tile_ring[n_local & 7] = none_left ? -1 : tile;
+        if (none_left) {
+          // pass the end marker to the MMA warp through the next stage's barrier (no bytes expected)
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (mbar_wait(&bars->empty[s], ph ^ 1, status)) mbar_arrive(&bars->full[s]);
+          break;
+        }
         const int m0 = (tile % tiles_m) * BM;
         const int n0 = (tile / tiles_m) * BN;
+        ++n_local;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -136,16 +155,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      while (ok) {
         const int acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
+        // the first stage of a tile also tells which tile it is
+        {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&bars->full[s], ph, status)) { ok = false; break; }
+        }
+        const int tile = *reinterpret_cast<volatile int*>(&bars->tile_ring[local_tile & 7]);
         if (!mbar_wait(&bars->acc_empty[acc], acc_ph ^ 1, status)) { ok = false; break; }
+        if (tile < 0) {
+          // no more tiles: release the epilogue warps (both arrivals of the accumulator barrier)
+          bars->acc_tile[acc] = -1;
+          mbar_arrive(&bars->acc_full[acc]);
+          mbar_arrive(&bars->acc_full[acc]);
+          break;
+        }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&bars->full[s], ph, status)) { ok = false; break; }
+          if (kb > 0 && !mbar_wait(&bars->full[s], ph, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
@@ -159,7 +192,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           umma_commit(&bars->empty[s]);       // frees the smem stage when the MMAs retire
         }
-        if (ok) umma_commit(&bars->acc_full[acc]);
+        if (ok) {
+          bars->acc_tile[acc] = tile;
+          mbar_arrive(&bars->acc_full[acc]);  // publishes acc_tile
+          umma_commit(&bars->acc_full[acc]);  // arrives when the accumulator is complete
+        }
+        ++local_tile;
       }
     }
   } else if (warp >= 4) {
@@ -167,12 +205,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int ew = warp - 4;                  // == warp % 4: TMEM lanes [32*ew, 32*ew+32)
     uint32_t local_tile = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-      const int m0 = (tile % tiles_m) * BM;
-      const int n0 = (tile / tiles_m) * BN;
+    for (;; ++local_tile) {
       const int acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, status)) { ok = false; break; }
+      const int tile = *reinterpret_cast<volatile int*>(&bars->acc_tile[acc]);
+      if (tile < 0) break;
+      const int m0 = (tile % tiles_m) * BM;
+      const int n0 = (tile / tiles_m) * BN;
       tc_fence_after();
       const int row = m0 + ew * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
@@ -233,6 +273,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem_base, ACC_BUFS * BN);
   }
+  if (sched != nullptr && threadIdx.x == 0) {
+    // the last CTA to leave rearms the scheduler slot for its next use
+    if (atomicAdd(&sched[1], 1) == static_cast<int>(gridDim.x) - 1) {
+      sched[0] = 0;
+      sched[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
+// Pool of tile-scheduler slots (next tile, finished CTAs), one slot per launch in rotation.  It is the only
+// device memory this library allocates by itself: 32 KiB, once per process.
+constexpr int kSchedSlots = 4096;
+
+int* next_sched_slot() {
+  static int* pool = nullptr;
+  static unsigned long long counter = 0;
+  static bool disabled = false;
+  if (disabled) return nullptr;
+  if (pool == nullptr) {
+    const char* env = getenv("PIPER_GEMM_STATIC_TILES");
+    if (env != nullptr && env[0] == '1') {
+      disabled = true;
+      return nullptr;
+    }
+    if (cudaMalloc(&pool, kSchedSlots * 2 * sizeof(int)) != cudaSuccess ||
+        cudaMemset(pool, 0, kSchedSlots * 2 * sizeof(int)) != cudaSuccess) {
+      pool = nullptr;
+      disabled = true;
+      return nullptr;
+    }
+  }
+  return pool + 2 * (counter++ % kSchedSlots);
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point, so the
@@ -293,7 +366,7 @@ static int launch(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& t
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, g.c, g.ldc, g.M, g.N, g.K, g.accumulate,
-                                                  g.status);
+                                                  g.status, next_sched_slot());
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

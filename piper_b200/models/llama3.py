@@ -76,10 +76,27 @@ class TransformerBlock(nn.Module):
         return h, self.feed_forward(y)
 
 
+def balanced_stage_layers(n_layers: int, num_stages: int, head_units: float = 2.3) -> list:
+    """Layers per stage when the last stage's LM head + loss cost about ``head_units`` transformer layers."""
+    left, out = n_layers + head_units, []
+    layers_left = n_layers
+    for s in range(num_stages - 1):
+        take = max(1, min(layers_left - (num_stages - 1 - s), round(left / (num_stages - s))))
+        out.append(take)
+        left -= take
+        layers_left -= take
+    out.append(layers_left)
+    return out
+
+
 class Transformer(nn.Module):
-    def __init__(self, cfg: LlamaConfig, seq_len: Optional[int] = None, num_stages: Optional[int] = None) -> None:
+    def __init__(self, cfg: LlamaConfig, seq_len: Optional[int] = None, num_stages: Optional[int] = None,
+                 stage_layers: Optional[list] = None) -> None:
+        """``stage_layers`` (layers per pipeline stage) overrides the equal split, e.g. to give the last stage,
+        which also runs the LM head and the loss, fewer layers."""
         super().__init__()
         self.cfg = cfg
+        self.stage_layers = list(stage_layers) if stage_layers else None
         self.seq_len = seq_len or cfg.max_seq_len
         if num_stages is None:
             from ..state import piper_metadata
@@ -107,8 +124,12 @@ class Transformer(nn.Module):
         n = len(self.layers)
         h = delta = None
         out = None
+        bounds = [0]
         for stage in range(self.num_stages):
-            lo, hi = stage * n // self.num_stages, (stage + 1) * n // self.num_stages
+            bounds.append(bounds[-1] + self.stage_layers[stage] if self.stage_layers
+                          else (stage + 1) * n // self.num_stages)
+        for stage in range(self.num_stages):
+            lo, hi = bounds[stage], bounds[stage + 1]
             with annotate("PP"):
                 if stage == 0:
                     h = self.tok_embeddings(tokens.reshape(-1))

@@ -134,6 +134,8 @@ class PiperActor:
         self.fused = None                   # parallel.fused.FusedCollectives when enabled
         self._channel_streams: dict = {}
         self._ep_splits: dict = {}          # (MB, PP, EP) -> split sizes shared by a layer's four token exchanges
+        self.time_nodes = False             # debug: CUDA-event and host time per DAG node kind, in node_times
+        self.last_host_time_s = 0.0
         self.debug_keep_grads = False       # tests: keep a scaled copy of the gradients each step
         self.last_grads: dict = {}
 
@@ -423,6 +425,7 @@ class DagExecutor:
         a = self.a
         self._works: dict[str, list] = {}
         t0 = time.perf_counter()
+        timed: list = []
         if self.cuda:
             # side streams must see the previous step's update before they touch parameters again
             cur = a.streams.get(DEFAULT_STREAM)
@@ -443,6 +446,10 @@ class DagExecutor:
             rf = torch.profiler.record_function(label) if (a.profile_nodes and label) else _NullCtx()
             with rf, (torch.cuda.stream(self._stream(node)) if self.cuda else _NullCtx()):
                 self._wait_preds(node)
+                t_node = time.perf_counter()
+                if a.time_nodes and self.cuda:
+                    ev0 = torch.cuda.Event(enable_timing=True)
+                    ev0.record(self._stream(node))
                 if kind == COMPUTE:
                     sub = node.compute_subkind
                     if sub == "FWD":
@@ -470,6 +477,14 @@ class DagExecutor:
                 elif kind == UPD:
                     self._update(node)
                 self._record(node)
+                if a.time_nodes:
+                    host_ms = (time.perf_counter() - t_node) * 1e3
+                    if self.cuda:
+                        ev1 = torch.cuda.Event(enable_timing=True)
+                        ev1.record(self._stream(node))
+                        timed.append((uid, node.compute_subkind or kind, ev0, ev1, host_ms))
+                    else:
+                        timed.append((uid, node.compute_subkind or kind, None, None, host_ms))
             if label is not None and not a.no_nvtx:
                 torch.cuda.nvtx.range_pop()
         for ws in self._works.values():
@@ -486,7 +501,20 @@ class DagExecutor:
             for s in a._channel_streams.values():
                 cur.wait_stream(s)
         a.last_losses = self.losses
-        return {"losses": self.losses, "host_time_s": time.perf_counter() - t0}
+        host_s = time.perf_counter() - t0
+        a.last_host_time_s = host_s
+        if a.time_nodes:
+            if self.cuda:
+                torch.cuda.synchronize()
+            per_kind: dict = {}
+            for uid, k, e0, e1, host_ms in timed:
+                rec = per_kind.setdefault(k, {"count": 0, "device_ms": 0.0, "host_ms": 0.0})
+                rec["count"] += 1
+                rec["host_ms"] += host_ms
+                if e0 is not None:
+                    rec["device_ms"] += e0.elapsed_time(e1)
+            a.node_times = per_kind
+        return {"losses": self.losses, "host_time_s": host_s}
 
     # ------------------------------------------------------------ compute
     def _forward(self, node: TrainingDAGNode) -> None:

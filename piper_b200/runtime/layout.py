@@ -118,7 +118,15 @@ class ProcessGroups:
             self._channel_tags[ch] = 1000 + i
             if self.backend == "nccl":
                 a, b = ch[0], ch[1]
-                pg = dist.new_group(ranks=sorted((a, b)), backend=self.backend, timeout=self.timeout)
+                # A posted receive waits on the GPU for its peer.  Keep the footprint of these kernels small: every
+                # SM they hold is an SM the persistent GEMM and attention kernels cannot use while they wait.
+                opts = dist.ProcessGroupNCCL.Options()
+                try:
+                    opts.config.max_ctas = int(os.environ.get("PIPER_P2P_MAX_CTAS", "8"))
+                    opts.config.min_ctas = 1
+                except Exception:
+                    pass
+                pg = dist.new_group(ranks=sorted((a, b)), backend=self.backend, timeout=self.timeout, pg_options=opts)
                 if self.layout.global_rank in (a, b):
                     self._channels[ch] = pg
 

@@ -314,3 +314,29 @@ def test_replicate_bucket_size_produces_bucket_chains_with_one_reduce_each():
     assert sorted(fwd) == sorted(f"s0.seg0{mb}.bucket{i}" for mb in ("", ".splitMB1") for i in (0, 1))
     reduces = [n for n in sub.nodes.values() if n.node_kind == "REDUCE_COMM"]
     assert len(reduces) == 4 and {n.node_meta["bucket_key"] for n in reduces} == {"s0.seg0.bucket0", "s0.seg0.bucket1"}
+
+
+def test_fx_json_roundtrip_of_traced_segments():
+    """Segments of the tiny Llama survive JSON serialisation and compute the same outputs."""
+    from piper_b200.compiler import fxserial
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.runtime.storage import materialize_module
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    model = Transformer(cfg, 32, 2)
+    model.load_const_attrs(32)
+    materialize_module(model)
+    x = torch.randint(0, cfg.vocab_size, (2, 32))
+    gm, inputs, ref = _capture(model, x)
+    _, segs = split_gm_by_annotations(gm)
+    vals = {n.name: v for n, v in zip([n for n in gm.graph.nodes if n.op == "placeholder"], inputs)}
+    prev = None
+    for s in segs:
+        clone = fxserial.loads(fxserial.dumps(s.gm))
+        phs = [p for p in clone.graph.nodes if p.op == "placeholder"]
+        acts = iter(() if prev is None else (prev if isinstance(prev, tuple) else (prev,)))
+        args = [vals[p.name] if p.name in vals else next(acts) for p in phs]
+        with torch.no_grad():
+            prev = clone(*args)
+    out = prev[0] if isinstance(prev, (tuple, list)) else prev
+    assert torch.allclose(out, ref, atol=1e-5)

@@ -191,3 +191,23 @@ def test_viz_outputs_and_trace_relabel(tmp_path):
     ]
     assert relabel_gpu_events(events) == 1
     assert events[2]["name"] == "FWD:MB=0,PP=0:uids0.seg0::gemm_kernel" and events[3]["name"] == "other"
+
+
+def test_artifact_dry_run_and_schedule_generator(tmp_path):
+    sys.path.insert(0, str(ROOT / "artifact" / "scripts"))
+    from make_piper_base_schedule import make_schedule
+    from piper_b200.compiler.schedule import derive_schedule_info
+
+    s = make_schedule(2, 2, zero=3, ep=True, virtual_stages=2, v_placement=True)
+    places = {d["filter"]["PP"]: d["devices"] for d in s if d["op"] == "place"}
+    assert places == {0: [0, 2], 1: [1, 3], 2: [1, 3], 3: [0, 2]}
+    assert all(d.get("shard_params") for d in s if d["op"] == "replicate")
+    info = derive_schedule_info(s + [{"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 4}], "x.json")
+    assert (info["num_stages"], info["pp_degree"], info["dp_degree"]) == (4, 2, 2)
+    out = subprocess.run([sys.executable, str(ROOT / "artifact" / "e2e_eval.py"), "--sweeps", "schedule", "--dry-run",
+                          "--systems", "piper,megatron", "--out", str(tmp_path)], capture_output=True, text=True,
+                         timeout=300, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-1500:]
+    assert out.stdout.count("test_harness.py") == 4 and "pretrain_gpt.py" in out.stdout
+    rows = list(__import__("csv").DictReader(open(next(tmp_path.glob("*/results.csv")))))
+    assert len(rows) == 8 and {r["schedule"] for r in rows} == {"1f1b", "interleaved_1f1b", "zerobubble", "dualpipev"}

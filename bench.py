@@ -172,6 +172,12 @@ def run_ours(args) -> dict:
     h2d = (x_host.numel() * x_host.element_size() if actor.has_first_stage() else 0) + \
           (y_host.numel() * y_host.element_size() if actor.has_loss_stage() else 0)
     d2h = 4 * len(last_losses or [])
+    loss_sum, loss_cnt = float(sum(last_losses or [])), float(len(last_losses or []))
+    if n > 1:
+        # whole-job figures: bytes copied by every rank per step, mean loss over the ranks that hold a loss stage
+        agg = torch.tensor([h2d, d2h, loss_sum, loss_cnt], device="cuda", dtype=torch.float64)
+        dist.all_reduce(agg)
+        h2d, d2h, loss_sum, loss_cnt = int(agg[0].item()), int(agg[1].item()), float(agg[2].item()), float(agg[3].item())
     return {
         "metric": "train tokens/sec (box, device-timed, max over ranks)", "value": value, "unit": "tokens/s",
         "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev / args.steps,
@@ -183,7 +189,7 @@ def run_ours(args) -> dict:
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "impl": "piper_b200", "loss": (sum(last_losses) / len(last_losses)) if last_losses else None,
+        "impl": "piper_b200", "loss": (loss_sum / loss_cnt) if loss_cnt else None,
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30, "host_ms_last_step": host_ms,
         "node_times_rank0": node_times,
     }

@@ -109,8 +109,8 @@ def piper_setup(model_class, model_args=(), model_kwargs: Optional[dict] = None,
         raise ValueError(f"model_dtype must be bfloat16 or float32, got {model_dtype}")
     if use_inductor:
         logger.info("use_inductor is ignored: stage graphs run the hand-written sm_100a kernels directly")
-    if activation_checkpointing:
-        logger.info("activation_checkpointing requested with num_checkpoints=%d", num_checkpoints)
+    if activation_checkpointing and num_checkpoints != 1:
+        logger.info("activation checkpointing works per graph segment; num_checkpoints=%d is not used", num_checkpoints)
     torch._dynamo.reset()
     api._reset_annotation_state()
 
@@ -180,6 +180,7 @@ def piper_setup(model_class, model_args=(), model_kwargs: Optional[dict] = None,
     _bind_channels(my_dag, layout.dp_rank)
     actor = PiperActor(layout, groups, dev, model_dtype, _adam_config(optim_fn, optim_kwargs), seed=seed,
                        no_nvtx=no_nvtx, baseline=baseline or os.environ.get("PIPER_BASELINE"))
+    actor.activation_checkpointing = bool(activation_checkpointing)
     actor.load_const_attrs(const_attrs or {})
     actor.load_training_dag(my_dag, n_mbs)
     if fused_collectives is None:

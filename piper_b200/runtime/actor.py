@@ -136,6 +136,7 @@ class PiperActor:
         self._ep_splits: dict = {}          # (MB, PP, EP) -> split sizes shared by a layer's four token exchanges
         self.time_nodes = False             # debug: CUDA-event and host time per DAG node kind, in node_times
         self.last_host_time_s = 0.0
+        self.activation_checkpointing = False   # forward keeps segment inputs only; backward recomputes the segment
         self.debug_keep_grads = False       # tests: keep a scaled copy of the gradients each step
         self.last_grads: dict = {}
 
@@ -528,9 +529,14 @@ class DagExecutor:
                 if t.is_floating_point():
                     t.requires_grad_(True)
             ins.append(t)
-        outs = bucket.gm(*bucket.build_args(ins))
+        if a.activation_checkpointing:
+            # keep only the segment's inputs; the backward node re-runs the segment with autograd on
+            with torch.no_grad():
+                outs = bucket.gm(*bucket.build_args(ins))
+        else:
+            outs = bucket.gm(*bucket.build_args(ins))
         outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
-        self.fwd_ctx[node.uid] = (ins, outs)
+        self.fwd_ctx[node.uid] = (ins, None if a.activation_checkpointing else outs)
         self.outs[node.uid] = outs
         self.shape_ref[node.uid] = [(tuple(o.shape), o.dtype) for o in outs
                                     if isinstance(o, torch.Tensor) and o.is_floating_point()]
@@ -561,6 +567,10 @@ class DagExecutor:
             st.alloc_grads()
         ins, outs = self.fwd_ctx.pop(fwd_uid)
         self.outs.pop(fwd_uid, None)
+        if outs is None:
+            # activation checkpointing: rebuild the autograd graph of this segment from its saved inputs
+            outs = bucket.gm(*bucket.build_args(ins))
+            outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
         if split:
             ops_core.wgrad_store.begin()
         try:

@@ -37,7 +37,7 @@ def _reference(batch, steps=1, lr=1e-3):
     return out
 
 
-def _worker(rank, world, schedule, num_stages, global_batch, dp, steps):
+def _worker(rank, world, schedule, num_stages, global_batch, dp, steps, ckpt=False):
     from piper_b200 import piper_exec_dag, piper_setup
     from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
     from piper_b200.nn import cross_entropy_loss
@@ -51,7 +51,7 @@ def _worker(rank, world, schedule, num_stages, global_batch, dp, steps):
     xs, ys = x[layout.dp_rank * per:(layout.dp_rank + 1) * per], y[layout.dp_rank * per:(layout.dp_rank + 1) * per]
     actor = piper_setup(Transformer, (cfg, SEQ, num_stages), optim_fn=torch.optim.Adam, example_inputs=[xs],
                         example_outputs=ys, model_dtype=torch.float32, const_attrs=Transformer.const_attrs(cfg, SEQ),
-                        schedule_directives=schedule, device="cpu")
+                        schedule_directives=schedule, device="cpu", activation_checkpointing=ckpt)
     actor.debug_keep_grads = True
     first = None
     for _ in range(steps):
@@ -100,6 +100,15 @@ def test_pp2_1f1b_matches_single_process(tmp_path):
 
     sched = _sched([[0], [1]], 4, order=build_1f1b_schedule(2, 4))
     res = run_ranks(2, _worker, (sched, 2, 8, 1, 1), tmp_path)
+    _check(res, _reference(8), dp=1)
+
+
+def test_pp2_zerobubble_with_activation_checkpointing(tmp_path):
+    """Forward keeps segment inputs only; backward (here the split BWD_I/BWD_W form) recomputes the segment."""
+    from piper_b200.compiler.builders import build_zerobubble_schedule
+
+    sched = _sched([[0], [1]], 4, order=build_zerobubble_schedule(2, 4))
+    res = run_ranks(2, _worker, (sched, 2, 8, 1, 1, True), tmp_path)
     _check(res, _reference(8), dp=1)
 
 

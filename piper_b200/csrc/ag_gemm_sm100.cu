@@ -5,14 +5,25 @@
 //
 // Same pipeline as the dense kernel (persistent CTAs, TMA producer warp,
 // single-thread tcgen05.mma issuer, two TMEM accumulators, four epilogue
-// warps).  The difference is the B operand: every 256-row weight tile is
-// fetched as four 64-row TMA boxes, each straight from the shard of the rank
-// that owns those rows - the local shard or a peer's over NVLink - through
-// one tensor map per rank.  The loads are ordinary (non-multicast) TMA
-// loads, so a remote tile crosses NVLink once per CTA that needs it while the
-// tensor cores work on the previous stage.  The CTAs of the first M tile
-// also store each weight box to the local full-size buffer (TMA store from
-// shared memory), so the backward GEMMs of the same bucket read local HBM.
+// warps) plus a gather warp per CTA.
+//
+// Gathered mode (a local full-size buffer is given): the gather warps of all
+// CTAs together pull every remote 64-row x 64-column weight box exactly once
+// over NVLink - a TMA load from the owner's shard into shared memory and a
+// TMA store into the local full buffer, several boxes in flight per CTA - and
+// count finished boxes per 256-row weight block in global memory.  Boxes are
+// handed out through one atomic counter in the order the GEMM needs them.
+// The GEMM walks weight blocks starting with the ones this rank owns (read
+// straight from its shard), so the tensor cores are busy while the first
+// remote blocks arrive; before it loads a block with remote rows the
+// producer waits, bounded, for that block's counter.  After all remote boxes
+// the gather warps copy the local shard into the full buffer as well, which
+// the backward GEMMs then read from local HBM.
+//
+// Direct mode (no full buffer): every weight box is loaded by TMA from the
+// shard of its owner by each CTA that needs it.
+//
+// All TMA loads are ordinary (non-multicast) loads.
 #include "gemm_sm100.h"
 #include "ptx.cuh"
 
@@ -29,14 +40,39 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int BOX_BYTES = 64 * BK * 2;
 constexpr int NUM_THREADS = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GATHER_BUFS = 4;                 // 8 KiB boxes staged per CTA; GATHER_BUFS - 1 loads in flight
+constexpr int GATHER_AHEAD = GATHER_BUFS - 1;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + GATHER_BUFS * BOX_BYTES + 1024 + 256;
+constexpr uint32_t kMaxReadyPolls = 1u << 20;  // x (100 ns sleep + one load): gives up after about a second
 
 struct Barriers {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t g_full[GATHER_BUFS];
   uint32_t tmem_base;
+  int g_block[8];            // weight block of the gather chunk in flight (-1: local copy, not counted)
+};
+
+// Geometry shared by the producer and the gather warp.
+struct Geo {
+  int N, rows_per_shard, num_peers, me, tiles_n, k_blocks, first_block;
+  __device__ int owner(int row) const {
+    const int p = row / rows_per_shard;
+    return p < num_peers ? p : num_peers - 1;
+  }
+  // position in the walk over weight blocks (own blocks first) -> block index
+  __device__ int block_at(int pos) const { return (first_block + pos) % tiles_n; }
+  // number of gather chunks the producer has to wait for before it may read this block from the full buffer
+  __device__ int needed(int nb) const {
+    int boxes = 0;
+    for (int j = 0; j < BN / 64; ++j) {
+      const int row = nb * BN + 64 * j;
+      if (row < N && owner(row) != me) ++boxes;
+    }
+    return boxes * k_blocks;
+  }
 };
 
 struct PeerMaps {
@@ -50,26 +86,40 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* s
                : "memory");
 }
 
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ PeerMaps peers,
                const __grid_constant__ CUtensorMap tmap_full, __nv_bfloat16* __restrict__ c, long long ldc, int M,
-               int N, int K, int rows_per_shard, int num_peers, int write_through, int* status) {
+               int N, int K, int rows_per_shard, int num_peers, int me, int gathered, int* scratch, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES);
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + STAGES * STAGE_BYTES + GATHER_BUFS * BOX_BYTES);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + BK - 1) / BK;
+  uint8_t* gbuf = smem + STAGES * STAGE_BYTES;             // gather staging boxes (1024-byte aligned)
+  Geo geo;
+  geo.N = N; geo.rows_per_shard = rows_per_shard; geo.num_peers = num_peers; geo.me = me;
+  geo.tiles_n = tiles_n; geo.k_blocks = k_blocks;
+  geo.first_block = gathered ? (me * rows_per_shard) / BN % tiles_n : 0;
+  int* gather_next = scratch;            // [0]: next gather chunk
+  int* ready = scratch + 2;              // [2 + block]: gathered chunks of that weight block
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
+    for (int b = 0; b < GATHER_BUFS; ++b) mbar_init(&bars->g_full[b], 1);
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->acc_full[a], 1);
       mbar_init(&bars->acc_empty[a], 4);
@@ -91,7 +141,25 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * BM;
-        const int n0 = (tile / tiles_m) * BN;
+        const int nb = geo.block_at(tile / tiles_m);
+        const int n0 = nb * BN;
+        if (gathered) {
+          // rows of other ranks are read from the local full buffer once the gather warps have delivered them
+          const int need = geo.needed(nb);
+          if (need > 0) {
+            uint32_t polls = 0;
+            while (ld_acquire_gpu(ready + nb) < need) {
+              if (++polls > kMaxReadyPolls || ((polls & 255u) == 0 && *reinterpret_cast<volatile int*>(status) != 0)) {
+                atomicCAS(status, 0, kStatusPeerTimeout);
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+            if (!ok) break;
+            asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy flag read -> async-proxy tile loads
+          }
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -109,7 +177,10 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               p = num_peers - 1;
               local = rows_per_shard + (row - num_peers * rows_per_shard);
             }
-            tma_load_2d(sb + j * BOX_BYTES, &peers.m[p], &bars->full[s], kb * BK, local);
+            if (gathered && (p != me || row >= N))
+              tma_load_2d(sb + j * BOX_BYTES, &tmap_full, &bars->full[s], kb * BK, row);
+            else
+              tma_load_2d(sb + j * BOX_BYTES, &peers.m[p], &bars->full[s], kb * BK, local);
           }
         }
       }
@@ -127,8 +198,6 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
-        const int m_tile = tile % tiles_m;
-        const int n0 = (tile / tiles_m) * BN;
         const int acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait(&bars->acc_empty[acc], acc_ph ^ 1, status)) { ok = false; break; }
@@ -139,7 +208,6 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&bars->full[s], ph, status)) { ok = false; break; }
           tc_fence_after();
-          uint8_t* sbp = smem + s * STAGE_BYTES + A_STAGE_BYTES;
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
@@ -149,19 +217,80 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             umma_bf16_ss(tmem_d, umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024),
                          umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          if (write_through && m_tile == 0) {
-            // keep a local copy of the gathered weight for the backward GEMMs
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              if (n0 + 64 * j < N) tma_store_2d(&tmap_full, sbp + j * BOX_BYTES, kb * BK, n0 + 64 * j);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          }
           umma_commit(&bars->empty[s]);
         }
         if (ok) umma_commit(&bars->acc_full[acc]);
       }
-      if (write_through) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------------ gather warp
+    if (lane == 0 && gathered) {
+      const int per_pass = tiles_n * (BN / 64) * k_blocks;
+      const int total = 2 * per_pass;        // pass 0: boxes of other ranks, pass 1: this rank's own boxes
+      uint32_t n = 0;                        // chunks whose load has been issued
+      int src_x[GATHER_BUFS] = {0, 0, 0, 0}, src_row[GATHER_BUFS] = {0, 0, 0, 0};
+      bool ok = true;
+      // chunk i: load at trip i, store at trip i + GATHER_AHEAD, counted at trip i + GATHER_AHEAD + 1
+      auto store_chunk = [&](uint32_t i) -> bool {
+        const int b = i % GATHER_BUFS;
+        if (!mbar_wait(&bars->g_full[b], (i / GATHER_BUFS) & 1, status)) return false;
+        tma_store_2d(&tmap_full, gbuf + b * BOX_BYTES, src_x[b], src_row[b]);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        return true;
+      };
+      auto count_chunk = [&](uint32_t i) {
+        const int nb = bars->g_block[i & 7];
+        if (nb >= 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");     // async-proxy stores -> generic-proxy counter
+          __threadfence();
+          atomicAdd(ready + nb, 1);
+        }
+      };
+      while (ok) {
+        if (*reinterpret_cast<volatile int*>(status) != 0) { ok = false; break; }
+        const int c = atomicAdd(gather_next, 1);
+        if (c >= total) break;
+        const int pass = c / per_pass;
+        const int rem = c - pass * per_pass;
+        const int q = rem / k_blocks;
+        const int kb = rem - q * k_blocks;
+        const int nb = geo.block_at(q / (BN / 64));
+        const int row = nb * BN + 64 * (q % (BN / 64));
+        if (row >= N) continue;
+        const int p = geo.owner(row);
+        if ((pass == 0) != (p != me)) continue;
+        const int b = n % GATHER_BUFS;
+        // the buffer's previous store (issued one trip ago) must have read it before it is overwritten
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        src_x[b] = kb * BK;
+        src_row[b] = row;
+        bars->g_block[n & 7] = p != me ? nb : -1;
+        mbar_arrive_expect_tx(&bars->g_full[b], BOX_BYTES);
+        tma_load_2d(gbuf + b * BOX_BYTES, &peers.m[p], &bars->g_full[b], kb * BK, row - p * rows_per_shard);
+        ++n;
+        if (n > GATHER_AHEAD) {
+          if (!store_chunk(n - 1 - GATHER_AHEAD)) { ok = false; break; }
+          if (n > GATHER_AHEAD + 1) {
+            asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // all but the newest store are complete
+            count_chunk(n - 2 - GATHER_AHEAD);
+          }
+        }
+      }
+      // drain: chunks [first_unstored, n) still sit in shared memory (or are on their way into it)
+      const uint32_t first_unstored = n > GATHER_AHEAD ? n - GATHER_AHEAD : 0;
+      uint32_t stored = first_unstored;
+      for (uint32_t i = first_unstored; i < n; ++i) {
+        if (ok && store_chunk(i)) {
+          stored = i + 1;
+        } else {
+          ok = false;
+          mbar_wait(&bars->g_full[i % GATHER_BUFS], (i / GATHER_BUFS) & 1, nullptr);   // let the load land
+        }
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      const uint32_t first_uncounted = first_unstored > 0 ? first_unstored - 1 : 0;
+      if (ok)
+        for (uint32_t i = first_uncounted; i < stored; ++i) count_chunk(i);
     }
   } else if (warp >= 4) {
     const int ew = warp - 4;
@@ -169,7 +298,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       const int m0 = (tile % tiles_m) * BM;
-      const int n0 = (tile / tiles_m) * BN;
+      const int n0 = geo.block_at(tile / tiles_m) * BN;
       const int acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, status)) { ok = false; break; }
@@ -216,7 +345,12 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 int ag_gemm_launch(const AgGemmArgs& g, int num_sms, cudaStream_t st) {
   if (g.num_peers < 1 || g.num_peers > kMaxPeers || g.rows_per_shard % 64 != 0 || g.K % 8 != 0) return -1;
+  if (g.my_index < 0 || g.my_index >= g.num_peers) return -1;
+  if (static_cast<long long>(g.num_peers) * g.rows_per_shard < g.N) return -1;
   if (g.M <= 0 || g.N <= 0) return 0;
+  const int tiles_n = (g.N + BN - 1) / BN;
+  const bool gathered = g.w_full != nullptr;
+  if (gathered && (g.scratch == nullptr || g.scratch_ints < tiles_n + 2)) return -1;
   CUtensorMap ta, tfull;
   PeerMaps pm;
   int rc;
@@ -230,8 +364,8 @@ int ag_gemm_launch(const AgGemmArgs& g, int num_sms, cudaStream_t st) {
       return rc;
   }
   for (int p = g.num_peers; p < kMaxPeers; ++p) pm.m[p] = pm.m[0];
-  const void* full = g.w_full != nullptr ? g.w_full : g.w_shards[0];
-  const long long full_rows = g.w_full != nullptr ? g.N : 1;
+  const void* full = gathered ? g.w_full : g.w_shards[g.my_index];
+  const long long full_rows = gathered ? g.N : 1;
   if ((rc = make_tmap_2d_bf16(&tfull, full, g.K, full_rows, static_cast<uint64_t>(g.K) * 2, BK, 64)) != 0) return rc;
   static bool configured = false;
   if (!configured) {
@@ -239,11 +373,12 @@ int ag_gemm_launch(const AgGemmArgs& g, int num_sms, cudaStream_t st) {
       return -2;
     configured = true;
   }
-  const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
+  if (gathered && cudaMemsetAsync(g.scratch, 0, sizeof(int) * (tiles_n + 2), st) != cudaSuccess) return -3;
+  const int tiles = ((g.M + BM - 1) / BM) * tiles_n;
   const int grid = tiles < num_sms ? tiles : num_sms;
   ag_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, pm, tfull, static_cast<__nv_bfloat16*>(g.y), g.N, g.M,
-                                                        g.N, g.K, g.rows_per_shard, g.num_peers,
-                                                        g.w_full != nullptr ? 1 : 0, g.status);
+                                                        g.N, g.K, g.rows_per_shard, g.num_peers, g.my_index,
+                                                        gathered ? 1 : 0, g.scratch, g.status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

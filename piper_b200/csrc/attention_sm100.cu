@@ -326,7 +326,9 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
   if (lane == 0) delta[((t / S) * Hq + h) * S + (t % S)] = s;
 }
 
-constexpr int BWD_THREADS = 192;
+// warps 0-3 and 6-9: two groups of 128 threads that split the columns of every S'/dP' tile; warp 4: TMA;
+// warp 5: MMA
+constexpr int BWD_THREADS = 320;
 
 template <int HD>
 struct BwdSmem {
@@ -394,10 +396,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       mbar_init(&bars->y_full[i], 1);
       mbar_init(&bars->y_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], 128);
+      mbar_init(&bars->s_empty[i], 256);
       mbar_init(&bars->v_full[i], 64);
     }
-    mbar_init(&bars->t_full, 128);
+    mbar_init(&bars->t_full, 256);
     mbar_init(&bars->t_empty, 1);
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
@@ -526,8 +528,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
     }
   } else {
     // ------------------------------------------- P' / dS' tiles + epilogue
-    const int row = threadIdx.x;   // stationary row == TMEM lane
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    // A warp reaches the TMEM lanes 32*(warp % 4)..+31; the two groups take columns [0,32) and [32,64).
+    const int wg = warp >= 6 ? 1 : 0;
+    const int row = (warp & 3) * 32 + lane;   // stationary row == TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int xpos = xb * 128 + row;   // position of this row inside the sequence
     float row_lse = 0.f, row_delta = 0.f;
     if (MODE == 0) {
@@ -542,7 +546,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       if (MODE == 1) {
         // Per-column lse/delta of the streamed query tile -> shared memory.
         const int hh = g * group + it / tiles_per_head;
-        if (row < 64) {
+        if (wg == 0 && row < 64) {
           const long long idx = (static_cast<long long>(b) * Hq + hh) * S + ti * 64 + row;
           vec[st * 128 + row] = lse[idx] * 1.4426950408889634f;
           vec[st * 128 + 64 + row] = delta[idx];
@@ -560,8 +564,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       const int ypos0 = ti * 64;
       const bool need_mask = (MODE == 0) ? (ypos0 + 63 > xb * 128) : (ypos0 < xb * 128 + 127);
       const uint32_t ts = tmem_base + lane_sel + st * 128;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      {
+        const int c = wg;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(ts + c * 32, sv);
         tmem_ld_32x32(ts + 64 + c * 32, dv);
@@ -607,7 +611,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         __nv_bfloat16* orow = (a == 0) ? o1 : o2;
         const float sc = (a == 0) ? scale : 1.f;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = wg; c < HD / 32; c += 2) {
           uint32_t r[32];
           tmem_ld_32x32(ta + c * 32, r);
           tmem_ld_wait();

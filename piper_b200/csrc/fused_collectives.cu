@@ -60,13 +60,42 @@ __device__ bool wait_flags(const uint64_t* flags, int n, unsigned long long epoc
 }
 
 constexpr int F1_THREADS = 256;
+// float4 vectors per thread per trip (all loads are issued before any use); fewer for large groups, whose
+// per-vector peer loads already keep enough bytes in flight
+__host__ __device__ constexpr int f1_unroll(int dp) { return dp <= 2 ? 4 : (dp <= 4 ? 2 : 1); }
 
+__device__ __forceinline__ float4 ld_stream_f4(const float* p) {
+  float4 r;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ void adam_vec(float4& g, float4& w, float4& mm, float4& vv, const AdamHyper& h) {
+  float* gp = reinterpret_cast<float*>(&g);
+  float* wp = reinterpret_cast<float*>(&w);
+  float* mp = reinterpret_cast<float*>(&mm);
+  float* vp = reinterpret_cast<float*>(&vv);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float gr = gp[k] * h.grad_scale;
+    mp[k] = h.beta1 * mp[k] + (1.f - h.beta1) * gr;
+    vp[k] = h.beta2 * vp[k] + (1.f - h.beta2) * gr * gr;
+    const float denom = sqrtf(vp[k] / h.bias_corr2) + h.eps;
+    wp[k] = wp[k] - h.lr * (mp[k] / h.bias_corr1) / denom - h.lr * h.weight_decay * wp[k];
+  }
+}
+
+// DP > 0: group size known at compile time (peer loops fully unrolled); DP == 0: any size.
+template <int DP>
 __global__ void __launch_bounds__(F1_THREADS)
 f1_kernel(const float* const* __restrict__ peer_grads, __nv_bfloat16* const* __restrict__ peer_params,
           uint64_t* const* __restrict__ peer_flags, float* __restrict__ master, float* __restrict__ m,
-          float* __restrict__ v, int my_rank, int dp, long long shard_numel, unsigned long long epoch,
+          float* __restrict__ v, int my_rank, int dp_rt, long long shard_numel, unsigned long long epoch,
           AdamHyper h, unsigned int* cta_counter, int* status, unsigned long long timeout_ns) {
   __shared__ int ok_s;
+  const int dp = DP > 0 ? DP : dp_rt;
   uint64_t* local_flags = peer_flags[my_rank];
   // ---- 1. publish "gradients final", wait for the peers
   if (threadIdx.x == 0) {
@@ -80,35 +109,73 @@ f1_kernel(const float* const* __restrict__ peer_grads, __nv_bfloat16* const* __r
   // ---- 2. reduce + Adam + parameter broadcast over this rank's shard
   const long long base = static_cast<long long>(my_rank) * shard_numel;
   const long long nvec = shard_numel / 4;
-  for (long long i = static_cast<long long>(blockIdx.x) * F1_THREADS + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * F1_THREADS) {
-    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = 0; p < dp; ++p) {
-      const float4 t = reinterpret_cast<const float4*>(peer_grads[p] + base)[i];
-      g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
-    }
-    float4 w = reinterpret_cast<float4*>(master)[i];
-    float4 mm = reinterpret_cast<float4*>(m)[i];
-    float4 vv = reinterpret_cast<float4*>(v)[i];
-    float* gp = reinterpret_cast<float*>(&g);
-    float* wp = reinterpret_cast<float*>(&w);
-    float* mp = reinterpret_cast<float*>(&mm);
-    float* vp = reinterpret_cast<float*>(&vv);
+  const long long stride = static_cast<long long>(gridDim.x) * F1_THREADS;
+  const long long first = static_cast<long long>(blockIdx.x) * F1_THREADS + threadIdx.x;
+  if (DP > 0) {
+    constexpr int NP = DP > 0 ? DP : 1;
+    constexpr int F1_UNROLL = f1_unroll(NP);
+    const float* gsrc[NP];
+    __nv_bfloat16* pdst[NP];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float gr = gp[k] * h.grad_scale;
-      mp[k] = h.beta1 * mp[k] + (1.f - h.beta1) * gr;
-      vp[k] = h.beta2 * vp[k] + (1.f - h.beta2) * gr * gr;
-      const float denom = sqrtf(vp[k] / h.bias_corr2) + h.eps;
-      wp[k] = wp[k] - h.lr * (mp[k] / h.bias_corr1) / denom - h.lr * h.weight_decay * wp[k];
+    for (int p = 0; p < NP; ++p) {
+      // start with the next rank's copy so that the ranks of a group do not all read the same peer at once
+      const int q = (my_rank + 1 + p) % NP;
+      gsrc[p] = peer_grads[q] + base;
+      pdst[p] = peer_params[q] + base;
     }
-    reinterpret_cast<float4*>(master)[i] = w;
-    reinterpret_cast<float4*>(m)[i] = mm;
-    reinterpret_cast<float4*>(v)[i] = vv;
-    uint2 packed;
-    packed.x = pack_bf16x2(wp[0], wp[1]);
-    packed.y = pack_bf16x2(wp[2], wp[3]);
-    for (int p = 0; p < dp; ++p) reinterpret_cast<uint2*>(peer_params[p] + base)[i] = packed;
+    for (long long i0 = first; i0 < nvec; i0 += stride * F1_UNROLL) {
+      float4 g[F1_UNROLL][NP], w[F1_UNROLL], mm[F1_UNROLL], vv[F1_UNROLL];
+#pragma unroll
+      for (int u = 0; u < F1_UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) {
+#pragma unroll
+          for (int p = 0; p < NP; ++p) g[u][p] = ld_stream_f4(gsrc[p] + 4 * i);
+          w[u] = ld_stream_f4(master + 4 * i);
+          mm[u] = ld_stream_f4(m + 4 * i);
+          vv[u] = ld_stream_f4(v + 4 * i);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < F1_UNROLL; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) {
+          float4 s = g[u][0];
+#pragma unroll
+          for (int p = 1; p < NP; ++p) {
+            s.x += g[u][p].x; s.y += g[u][p].y; s.z += g[u][p].z; s.w += g[u][p].w;
+          }
+          adam_vec(s, w[u], mm[u], vv[u], h);
+          reinterpret_cast<float4*>(master)[i] = w[u];
+          reinterpret_cast<float4*>(m)[i] = mm[u];
+          reinterpret_cast<float4*>(v)[i] = vv[u];
+          uint2 packed;
+          packed.x = pack_bf16x2(w[u].x, w[u].y);
+          packed.y = pack_bf16x2(w[u].z, w[u].w);
+#pragma unroll
+          for (int p = 0; p < NP; ++p) reinterpret_cast<uint2*>(pdst[p])[i] = packed;
+        }
+      }
+    }
+  } else {
+    for (long long i = first; i < nvec; i += stride) {
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < dp; ++p) {
+        const float4 t = ld_stream_f4(peer_grads[p] + base + 4 * i);
+        g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+      }
+      float4 w = reinterpret_cast<float4*>(master)[i];
+      float4 mm = reinterpret_cast<float4*>(m)[i];
+      float4 vv = reinterpret_cast<float4*>(v)[i];
+      adam_vec(g, w, mm, vv, h);
+      reinterpret_cast<float4*>(master)[i] = w;
+      reinterpret_cast<float4*>(m)[i] = mm;
+      reinterpret_cast<float4*>(v)[i] = vv;
+      uint2 packed;
+      packed.x = pack_bf16x2(w.x, w.y);
+      packed.y = pack_bf16x2(w.z, w.w);
+      for (int p = 0; p < dp; ++p) reinterpret_cast<uint2*>(peer_params[p] + base)[i] = packed;
+    }
   }
 
   // ---- 3. last CTA publishes "done"; everyone waits for the peers' "done"
@@ -129,9 +196,8 @@ f1_kernel(const float* const* __restrict__ peer_grads, __nv_bfloat16* const* __r
   float4* lg = reinterpret_cast<float4*>(const_cast<float*>(peer_grads[my_rank]));
   const long long total_vec = shard_numel * dp / 4;
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (long long i = static_cast<long long>(blockIdx.x) * F1_THREADS + threadIdx.x; i < total_vec;
-       i += static_cast<long long>(gridDim.x) * F1_THREADS)
-    lg[i] = z;
+#pragma unroll 4
+  for (long long i = first; i < total_vec; i += stride) lg[i] = z;
 }
 
 // ===================================================================== F3
@@ -175,20 +241,31 @@ __global__ void ep_dispatch_push_kernel(const __nv_bfloat16* __restrict__ x, con
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long w0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int vecs = D / 8;                      // 16-byte vectors per row
   for (long long t = w0; t < T; t += warps) {
+    // lanes 0..k-1 each reserve the destination row of one of the token's k copies
+    int d_l = 0, row_l = 0;
+    if (lane < k) {
+      const int e = idx[t * k + lane];
+      d_l = e / experts_local;
+      row_l = my_rank * cap + seg_off[e] + atomicAdd(cursor + e, 1);
+      pos[t * k + lane] = d_l * (ep * cap) + row_l;
+    }
     const uint4* src = reinterpret_cast<const uint4*>(x + t * D);
-    for (int j = 0; j < k; ++j) {
-      int d = 0, row = 0;
-      if (lane == 0) {
-        const int e = idx[t * k + j];
-        d = e / experts_local;
-        row = my_rank * cap + seg_off[e] + atomicAdd(cursor + e, 1);
-        pos[t * k + j] = d * (ep * cap) + row;
+    // the row is read once (four vectors per lane per trip) and stored k times
+    for (int i0 = lane; i0 < vecs; i0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + 32 * u < vecs) v[u] = src[i0 + 32 * u];
+      for (int j = 0; j < k; ++j) {
+        const int d = __shfl_sync(0xffffffffu, d_l, j);
+        const int row = __shfl_sync(0xffffffffu, row_l, j);
+        uint4* dst = reinterpret_cast<uint4*>(peer_recv[d] + static_cast<long long>(row) * D);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i0 + 32 * u < vecs) dst[i0 + 32 * u] = v[u];
       }
-      d = __shfl_sync(0xffffffffu, d, 0);
-      row = __shfl_sync(0xffffffffu, row, 0);
-      uint4* dst = reinterpret_cast<uint4*>(peer_recv[d] + static_cast<long long>(row) * D);
-      for (int i = lane; i < D / 8; i += 32) dst[i] = src[i];
     }
   }
   // zero the padding rows of every segment this rank owns in the peers' regions
@@ -256,28 +333,59 @@ __global__ void ep_combine_pull_kernel(const __nv_bfloat16* const* __restrict__ 
   const int lane = threadIdx.x & 31;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long region = static_cast<long long>(ep) * cap;
+  const int vecs = D / 8;
   for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
-    for (int i = lane; i < D / 8; i += 32) {
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int j = 0; j < k; ++j) {
-        const int p = pos[t * k + j];
-        const int d = static_cast<int>(p / region);
-        const long long row = p % region;
-        const float w = weights[t * k + j];
-        const uint4 q = reinterpret_cast<const uint4*>(peer_out[d] + row * D)[i];
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+    // lanes 0..k-1 hold the location and the router weight of one expert output each
+    const __nv_bfloat16* src_l = nullptr;
+    float w_l = 0.f;
+    if (lane < k) {
+      const int p = pos[t * k + lane];
+      src_l = peer_out[static_cast<int>(p / region)] + (p % region) * D;
+      w_l = weights[t * k + lane];
+    }
+    for (int i0 = lane; i0 < vecs; i0 += 64) {
+      const bool two = i0 + 32 < vecs;
+      float acc[2][8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float2 f = __bfloat1622float2(h[c]);
-          acc[2 * c] += w * f.x;
-          acc[2 * c + 1] += w * f.y;
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[u][c] = 0.f;
+      // four expert outputs at a time: eight 16-byte peer loads in flight per lane before the first use
+      for (int j0 = 0; j0 < k; j0 += 4) {
+        uint4 q[4][2];
+        float w[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = j0 + jj < k ? j0 + jj : k - 1;
+          const uint4* row = reinterpret_cast<const uint4*>(
+              __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(src_l), j));
+          w[jj] = __shfl_sync(0xffffffffu, w_l, j);
+          if (j0 + jj >= k) w[jj] = 0.f;           // past the last expert: the clamped row is read but not used
+          q[jj][0] = row[i0];
+          q[jj][1] = two ? row[i0 + 32] : make_uint4(0, 0, 0, 0);
         }
-      }
-      uint4 o;
-      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) oh[c] = __floats2bfloat162_rn(acc[2 * c], acc[2 * c + 1]);
-      reinterpret_cast<uint4*>(out + t * D)[i] = o;
+        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[jj][u]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float2 f = __bfloat1622float2(h[c]);
+              acc[u][2 * c] += w[jj] * f.x;
+              acc[u][2 * c + 1] += w[jj] * f.y;
+            }
+          }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (u == 1 && !two) break;
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) oh[c] = __floats2bfloat162_rn(acc[u][2 * c], acc[u][2 * c + 1]);
+        reinterpret_cast<uint4*>(out + t * D)[i0 + 32 * u] = o;
+      }
     }
   }
 }
@@ -290,9 +398,18 @@ int f1_rs_adam_ag(const float* const* peer_grads, void* const* peer_params, uint
                   unsigned long long timeout_ns, int num_ctas, cudaStream_t st) {
   if (shard_numel % 4 != 0 || dp < 1) return -1;
   if (shard_numel == 0) return 0;
-  f1_kernel<<<num_ctas, F1_THREADS, 0, st>>>(peer_grads, reinterpret_cast<__nv_bfloat16* const*>(peer_params),
-                                            peer_flags, master, m, v, my_rank, dp, shard_numel, epoch, h,
-                                            cta_counter, status, timeout_ns);
+  auto pp = reinterpret_cast<__nv_bfloat16* const*>(peer_params);
+#define PIPER_F1_LAUNCH(DPV)                                                                                   \
+  f1_kernel<DPV><<<num_ctas, F1_THREADS, 0, st>>>(peer_grads, pp, peer_flags, master, m, v, my_rank, dp,        \
+                                                  shard_numel, epoch, h, cta_counter, status, timeout_ns)
+  switch (dp) {
+    case 1: PIPER_F1_LAUNCH(1); break;
+    case 2: PIPER_F1_LAUNCH(2); break;
+    case 4: PIPER_F1_LAUNCH(4); break;
+    case 8: PIPER_F1_LAUNCH(8); break;
+    default: PIPER_F1_LAUNCH(0); break;
+  }
+#undef PIPER_F1_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -304,7 +421,7 @@ int ep_dispatch_push(const void* x, const int* idx, const int* counts, int* seg_
                      void* const* peer_recv, int* const* peer_meta, uint64_t* const* peer_flags,
                      unsigned int* cta_counter, int my_rank, int ep, int experts_local, long long T, int D, int k,
                      int cap, unsigned long long epoch, int num_ctas, cudaStream_t st) {
-  if (D % 8 != 0 || ep < 1 || experts_local < 1) return -1;
+  if (D % 8 != 0 || ep < 1 || experts_local < 1 || k < 1 || k > 32) return -1;
   ep_prepare_kernel<<<1, 32, 0, st>>>(counts, seg_off, peer_meta, my_rank, ep, experts_local);
   ep_dispatch_push_kernel<<<num_ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), idx, counts, seg_off, cursor,
                                                     pos, reinterpret_cast<__nv_bfloat16* const*>(peer_recv),
@@ -329,7 +446,7 @@ int ep_signal(uint64_t* const* peer_flags, int slot0, int my_rank, int ep, unsig
 int ep_combine_pull(const void* const* peer_out, const int* pos, const float* weights, void* out,
                     const uint64_t* out_flags, long long T, int D, int k, int ep, int cap, unsigned long long epoch,
                     unsigned long long timeout_ns, int* status, int num_ctas, cudaStream_t st) {
-  if (D % 8 != 0) return -1;
+  if (D % 8 != 0 || k < 1 || k > 32) return -1;
   ep_combine_pull_kernel<<<num_ctas, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16* const*>(peer_out), pos,
                                                    weights, static_cast<__nv_bfloat16*>(out), out_flags, T, D, k, ep,
                                                    cap, epoch, timeout_ns, status);

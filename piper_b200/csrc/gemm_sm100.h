@@ -69,15 +69,21 @@ constexpr int kMaxPeers = 8;
 
 // Y[M, N] = X[M, K] * W[N, K]^T with W sharded by rows: w_shards[p] points at
 // rank p's rows [p*rows_per_shard, (p+1)*rows_per_shard) (local or peer-mapped
-// memory, rows_per_shard a multiple of 64).  When w_full is not null the
-// gathered weight is also written there ([N, K], local memory).
+// memory, rows_per_shard a multiple of 64); shard my_index is this rank's own.
+// When w_full is not null every remote row crosses NVLink once, into w_full
+// ([N, K], local memory, complete when the kernel ends), and scratch must
+// point at scratch_ints >= ceil(N / 256) + 2 ints of device memory that no
+// other launch in flight uses.  When w_full is null each CTA loads the weight
+// boxes it needs straight from their owners.
 struct AgGemmArgs {
   const void* x;
   const void* w_shards[kMaxPeers];
   void* w_full;
   void* y;
   int M, N, K;
-  int rows_per_shard, num_peers;
+  int rows_per_shard, num_peers, my_index;
+  int* scratch;
+  int scratch_ints;
   int* status;
 };
 

@@ -101,9 +101,11 @@ class FusedCollectives:
 class ShardedWeight:
     """A weight ``[N, K]`` sharded by rows over a group, each shard in symmetric memory.
 
-    ``linear(x)`` computes ``x @ W^T`` with one kernel that fetches every weight tile from the rank that owns
-    it (local HBM or a peer over NVLink) while the tensor cores work on the previous tile; with
-    ``keep_full=True`` the gathered weight is also written to a local ``[N, K]`` buffer for the backward GEMMs.
+    ``linear(x)`` computes ``x @ W^T`` with one kernel.  With ``keep_full=True`` gather warps inside the GEMM
+    pull every remote weight row once over NVLink into a local ``[N, K]`` buffer while the tensor cores start on
+    the rows this rank owns; the GEMM reads remote rows from that buffer as they arrive, and the backward GEMMs
+    use it afterwards.  With ``keep_full=False`` each CTA loads the weight tiles it needs straight from their
+    owners (more NVLink traffic, no extra memory).
     """
 
     def __init__(self, full_weight: torch.Tensor, ranks: list, group, keep_full: bool = True) -> None:
@@ -120,14 +122,17 @@ class ShardedWeight:
         if hi > lo:
             self.shard[:hi - lo].copy_(full_weight[lo:hi])
         self.full = torch.empty((N, K), dtype=torch.bfloat16, device=full_weight.device) if keep_full else None
+        # gather bookkeeping of the kernel (next chunk, per-block arrival counters); cleared by every launch
+        self.scratch = torch.zeros((N + 255) // 256 + 2, dtype=torch.int32, device=full_weight.device) \
+            if keep_full else None
         torch.cuda.synchronize()
         dist.barrier(group=group)
 
     def linear(self, x: torch.Tensor) -> torch.Tensor:
         x2 = x.reshape(-1, self.K).contiguous()
         y = torch.empty((x2.shape[0], self.N), dtype=torch.bfloat16, device=x.device)
-        native.lib().ag_gemm(x2, [int(p) for p in self.buf.ptrs], self.full, y, self.N, self.rows_per_shard,
-                             native.status_tensor(x.device))
+        native.lib().ag_gemm(x2, [int(p) for p in self.buf.ptrs], self.index, self.full, self.scratch, y, self.N,
+                             self.rows_per_shard, native.status_tensor(x.device))
         return y.view(*x.shape[:-1], self.N)
 
 

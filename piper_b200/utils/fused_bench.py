@@ -70,7 +70,7 @@ def main():
         lib.f1_rs_adam_ag(buf.offset_ptrs(g_off), buf.offset_ptrs(0), buf.offset_ptrs(f_off), master, m, v, rank,
                           world, epoch[0], 1e-4, 0.9, 0.95, 1e-8, 0.0, epoch[0], 1.0, counter, st, 30.0, ctas)
 
-    for ctas in (64, 148, 296, 592):
+    for ctas in (148, 296, 592, 1184):
         grads.normal_()
         ms = _median_ms(lambda: f1(ctas))
         inbound = (world - 1) * shard * 4            # peers' gradient slices read by this rank
@@ -129,20 +129,22 @@ def main():
     def f3_dispatch():
         state["r"] = ex.dispatch(xt, idx, counts)
 
-    ms_d = _median_ms(f3_dispatch)
-    pos = state["r"][1]
-
-    def f3_combine():
-        ex.epoch += 1          # every rank publishes and waits for the same new epoch
-        return ex.combine(pos, weights, T)
-
-    ms_c = _median_ms(f3_combine)
     nv = (world - 1) / world * T * k * D * 2
     roof = nv / (NVLINK_GBS * 1e6)
-    rows.append({"path": "F3 dispatch push", "world": world, "ms": ms_d, "roofline_ms": roof,
-                 "fraction_of_roofline": roof / ms_d, "nvlink_GBs": nv / ms_d / 1e6})
-    rows.append({"path": "F3 combine pull", "world": world, "ms": ms_c, "roofline_ms": roof,
-                 "fraction_of_roofline": roof / ms_c, "nvlink_GBs": nv / ms_c / 1e6})
+    for ctas in (128, 296, 592):
+        ex.num_ctas = ctas
+        ms_d = _median_ms(f3_dispatch)
+        pos = state["r"][1]
+
+        def f3_combine():
+            ex.epoch += 1          # every rank publishes and waits for the same new epoch
+            return ex.combine(pos, weights, T)
+
+        ms_c = _median_ms(f3_combine)
+        rows.append({"path": "F3 dispatch push", "ctas": ctas, "world": world, "ms": ms_d, "roofline_ms": roof,
+                     "fraction_of_roofline": roof / ms_d, "nvlink_GBs": nv / ms_d / 1e6})
+        rows.append({"path": "F3 combine pull", "ctas": ctas, "world": world, "ms": ms_c, "roofline_ms": roof,
+                     "fraction_of_roofline": roof / ms_c, "nvlink_GBs": nv / ms_c / 1e6})
     native.check_status()
     if rank == 0:
         for r in rows:

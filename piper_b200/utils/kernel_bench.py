@@ -37,7 +37,15 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--only", default=None, help="run one family on one shape, e.g. gemm:ffn_up, attn, elementwise")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-cublas", action="store_true", help="skip the library GEMM comparison")
     args = ap.parse_args(argv)
+    global _time
+    _base_time = _time
+    _time = lambda fn, flush=None: _base_time(fn, iters=args.iters, warmup=args.warmup, flush=flush)  # noqa: E731
+    only_family, _, only_shape = (args.only or "").partition(":")
     from piper_b200 import ops
     from piper_b200.ops import native
 
@@ -50,12 +58,14 @@ def main(argv=None):
               ("ffn_down", T, 4096, 14336), ("lm_head", T, 128256, 4096), ("square8k", 8192, 8192, 8192)]
     if args.quick:
         shapes = shapes[:2]
+    if only_family:
+        shapes = [sh for sh in shapes if only_family == "gemm" and (not only_shape or sh[0] == only_shape)]
     for name, M, N, K in shapes:
         a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
         c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         ms = _time(lambda: native.lib().gemm(a, b, c, False, False, False, st), flush=flush)
-        ms_ref = _time(lambda: torch.matmul(a, b.t(), out=c), flush=flush)
+        ms_ref = float("nan") if args.no_cublas else _time(lambda: torch.matmul(a, b.t(), out=c), flush=flush)
         fl = 2.0 * M * N * K
         rows.append({"kernel": f"gemm_fwd:{name}", "ms": ms, "tflops": fl / ms / 1e9, "cublas_ms": ms_ref,
                      "cublas_tflops": fl / ms_ref / 1e9})
@@ -68,7 +78,10 @@ def main(argv=None):
         ms = _time(lambda: native.lib().gemm(dy, a, dw, True, True, True, st), flush=flush)
         rows.append({"kernel": f"gemm_wgrad_f32acc:{name}", "ms": ms, "tflops": fl / ms / 1e9})
         del a, b, c, dy, dx, dw
-    for (B, S, Hq, Hkv, hd) in [(1, 4096, 32, 8, 128), (1, 4096, 32, 4, 128)]:
+    attn_shapes = [(1, 4096, 32, 8, 128), (1, 4096, 32, 4, 128)]
+    if only_family and only_family != "attn":
+        attn_shapes = []
+    for (B, S, Hq, Hkv, hd) in attn_shapes:
         qkv = torch.randn(B * S, (Hq + 2 * Hkv) * hd, device=dev, dtype=torch.bfloat16).requires_grad_(True)
         out = ops.attention(qkv, B, S, Hq, Hkv, hd)
         g = torch.randn_like(out)
@@ -82,6 +95,8 @@ def main(argv=None):
             o.backward(g)
         ms_fb = _time(bwd, flush=flush)
         rows.append({"kernel": f"attn_fwd+bwd:Hq{Hq}kv{Hkv}", "ms": ms_fb, "tflops": 3.5 * fl / ms_fb / 1e9})
+    if only_family and only_family != "elementwise":
+        return _finish(rows, args, native)
     x = torch.randn(T, 4096, device=dev, dtype=torch.bfloat16)
     w = torch.randn(4096, device=dev, dtype=torch.bfloat16)
     ms = _time(lambda: ops.rmsnorm(x, w), flush=flush)
@@ -93,6 +108,10 @@ def main(argv=None):
     labels = torch.randint(0, 128256, (T,), device=dev)
     ms = _time(lambda: ops.cross_entropy(logits, labels), flush=flush)
     rows.append({"kernel": "ce_fwd:4096x128256", "ms": ms, "gbs": logits.numel() * 2 / ms / 1e6})
+    return _finish(rows, args, native)
+
+
+def _finish(rows, args, native):
     native.check_status()
     for r in rows:
         print(json.dumps(r))

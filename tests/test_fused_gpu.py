@@ -111,7 +111,28 @@ def _f2_f3_worker(rank, world):
     ref = x.float() @ w.float().t()
     out["f2_rel"] = ((y.float() - ref).norm() / ref.norm()).item()
     out["f2_full_equal"] = bool(torch.equal(sw.full, w))
+    # second launch on the same object (scratch counters are reused), then the direct mode without a full buffer
+    sw.full.zero_()
+    y2 = sw.linear(x)
+    torch.cuda.synchronize()
+    native.check_status()
+    out["f2_repeat_equal"] = bool(torch.equal(y2, y)) and bool(torch.equal(sw.full, w))
     dist.barrier()
+    del sw
+    N2, K2, T2 = 2304, 1024, 640               # several weight blocks and row tiles per rank
+    w2 = (torch.randn(N2, K2, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    x2 = torch.randn(T2, K2, generator=g).to(torch.bfloat16).to(dev)
+    ref2 = x2.float() @ w2.float().t()
+    for keep in (True, False):
+        sw2 = ShardedWeight(w2, ranks, None, keep_full=keep)
+        yk = sw2.linear(x2)
+        torch.cuda.synchronize()
+        native.check_status()
+        out[f"f2_rel_big_{keep}"] = ((yk.float() - ref2).norm() / ref2.norm()).item()
+        if keep:
+            out["f2_full_equal"] = out["f2_full_equal"] and bool(torch.equal(sw2.full, w2))
+        dist.barrier()
+        del sw2
     # ---- F3: dispatch push -> (identity expert x2) -> combine pull
     Tt, D, E, k = 512, 256, 8, 2
     g2 = torch.Generator(device="cpu").manual_seed(100 + rank)
@@ -146,7 +167,37 @@ def test_f2_ag_gemm_and_f3_dispatch_combine_on_two_gpus(tmp_path):
 
     res = run_ranks(2, _f2_f3_worker, (), tmp_path, timeout=600)
     for r in res:
-        assert r["f2_rel"] < 1e-2 and r["f2_full_equal"], r
+        assert r["f2_rel"] < 1e-2 and r["f2_full_equal"] and r["f2_repeat_equal"], r
+        assert r["f2_rel_big_True"] < 1e-2 and r["f2_rel_big_False"] < 1e-2, r
         for it in range(2):
             assert r[f"f3_counts_ok_{it}"], r
             assert r[f"f3_rel_{it}"] < 1.5e-2, r
+
+
+@pytest.mark.parametrize("me", [0, 1, 2])
+def test_f2_gathered_mode_with_local_shards_on_one_gpu(me):
+    """The gather path of the all-gather GEMM, with every shard in this GPU's own memory (three "ranks")."""
+    from piper_b200.ops import native
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    N, K, T, shards = 1664, 640, 300, 3       # shards of 576 rows: 256-row weight blocks straddle shard boundaries
+    rows = ((N + shards - 1) // shards + 63) // 64 * 64
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).to(dev)
+    parts = []
+    for p in range(shards):
+        s_ = torch.zeros(rows, K, dtype=torch.bfloat16, device=dev)
+        lo, hi = p * rows, min((p + 1) * rows, N)
+        if hi > lo:
+            s_[:hi - lo].copy_(w[lo:hi])
+        parts.append(s_)
+    full = torch.zeros(N, K, dtype=torch.bfloat16, device=dev)
+    scratch = torch.zeros((N + 255) // 256 + 2, dtype=torch.int32, device=dev)
+    y = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+    native.lib().ag_gemm(x, [p.data_ptr() for p in parts], me, full, scratch, y, N, rows, native.status_tensor(dev))
+    torch.cuda.synchronize()
+    native.check_status()
+    ref = x.float() @ w.float().t()
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+    assert torch.equal(full, w)

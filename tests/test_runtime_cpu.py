@@ -211,3 +211,41 @@ def test_artifact_dry_run_and_schedule_generator(tmp_path):
     assert out.stdout.count("test_harness.py") == 4 and "pretrain_gpt.py" in out.stdout
     rows = list(__import__("csv").DictReader(open(next(tmp_path.glob("*/results.csv")))))
     assert len(rows) == 8 and {r["schedule"] for r in rows} == {"1f1b", "interleaved_1f1b", "zerobubble", "dualpipev"}
+
+
+def test_baseline_runners_dry_run_and_padded_bmm_hook():
+    """Megatron runner builds its command without Megatron; DeepSpeed runner reports the missing package; the
+    TorchTitan hook's padded batched-matmul experts equal a per-expert loop."""
+    import importlib.util
+    import subprocess
+
+    import torch.nn.functional as F
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "artifact", "run_megatron.py"), "--nnodes", "1",
+                          "--nproc-per-node", "8", "--pp", "4", "--dp", "2", "--model", "qwen3_9b", "--dry-run"],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and "--pipeline-model-parallel-size 4" in out.stdout and "--num-experts 64" in out.stdout
+    bad = subprocess.run([sys.executable, os.path.join(root, "artifact", "run_megatron.py"), "--nnodes", "1",
+                          "--nproc-per-node", "8", "--pp", "4", "--dp", "1", "--dry-run"],
+                         capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0 and "does not match" in bad.stderr
+    if importlib.util.find_spec("deepspeed") is None:
+        ds = subprocess.run([sys.executable, os.path.join(root, "artifact", "run_deepspeed.py"), "--pp", "2"],
+                            capture_output=True, text=True, timeout=300)
+        assert ds.returncode == 3 and "not installed" in ds.stderr
+
+    spec = importlib.util.spec_from_file_location("artifact_site", os.path.join(root, "artifact", "sitecustomize.py"))
+    hook = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(hook)
+    g = torch.Generator().manual_seed(3)
+    E, d, f = 4, 16, 8
+    w1, w3, w2 = torch.randn(E, f, d, generator=g), torch.randn(E, f, d, generator=g), torch.randn(E, d, f, generator=g)
+    counts, x = torch.tensor([3, 0, 5, 2]), torch.randn(10, d, generator=g)
+    got = hook._padded_bmm_experts(w1, w2, w3, x, counts)
+    want, s = torch.zeros_like(x), 0
+    for e, n in enumerate(counts.tolist()):
+        r = x[s:s + n]
+        want[s:s + n] = (F.silu(r @ w1[e].t()) * (r @ w3[e].t())) @ w2[e].t()
+        s += n
+    assert torch.allclose(got, want, atol=1e-5)

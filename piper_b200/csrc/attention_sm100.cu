@@ -54,7 +54,9 @@ __device__ __forceinline__ void store_row_chunk_sw128(uint8_t* tile, int row, in
 }
 
 // ================================================================= forward
-constexpr int FWD_THREADS = 192;
+// warps 0-3 and 6-9: two softmax groups of 128 threads (each takes half the key columns of every score
+// tile and half the head dimension of the output); warp 4: TMA; warp 5: MMA
+constexpr int FWD_THREADS = 320;
 
 template <int HD>
 struct FwdSmem {
@@ -65,7 +67,8 @@ struct FwdSmem {
   static constexpr int K_OFF = TILE;            // 2 stages
   static constexpr int V_OFF = 3 * TILE;        // 2 stages
   static constexpr int P_OFF = 5 * TILE;
-  static constexpr int BAR_OFF = P_OFF + P_BYTES;
+  static constexpr int X_OFF = P_OFF + P_BYTES;   // row-max exchange [2 tiles][2 groups][128] + row-sum [2][128]
+  static constexpr int BAR_OFF = X_OFF + 6 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -75,6 +78,7 @@ struct FwdBars {
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full, p_empty;
   uint64_t o_full[2], o_empty[2];
+  uint64_t mx_full[2], l_full;        // the two softmax groups exchange row maxima / row sums
   uint32_t tmem_base;
 };
 
@@ -102,12 +106,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       mbar_init(&bars->kv_full[i], 1);
       mbar_init(&bars->kv_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], 128);
+      mbar_init(&bars->s_empty[i], 256);
       mbar_init(&bars->o_full[i], 1);
-      mbar_init(&bars->o_empty[i], 128);
+      mbar_init(&bars->o_empty[i], 256);
+      mbar_init(&bars->mx_full[i], 256);
     }
-    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->p_full, 256);
     mbar_init(&bars->p_empty, 1);
+    mbar_init(&bars->l_full, 256);
     fence_mbar_init();
     tma_prefetch_desc(&tmap);
   }
@@ -194,11 +200,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
     }
   } else {
     // --------------------------------------------------- softmax + output
-    const int row = threadIdx.x;                 // 0..127 == TMEM lane
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
-    float o_acc[HD];
+    // A warp reaches the TMEM lanes 32*(warp % 4)..+31.  Group wg owns key columns [64*wg, 64*wg + 64) of every
+    // score tile and output columns [wg*HD/2, (wg+1)*HD/2); per tile the groups exchange their row maxima.
+    constexpr int HH = HD / 2;
+    const int wg = warp >= 6 ? 1 : 0;
+    const int row = (warp & 3) * 32 + lane;      // query row == TMEM lane
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float* xbuf = reinterpret_cast<float*>(smem + L::X_OFF);
+    float o_acc[HH];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o_acc[i] = 0.f;
+    for (int i = 0; i < HH; ++i) o_acc[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks && ok; ++j) {
@@ -206,52 +217,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       const bool diag = (j == qblk);
       if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1, status)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t ts = tmem_s + lane_sel + s * 128;
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
+      const uint32_t ts = tmem_s + lane_sel + s * 128 + wg * 64;
+      uint32_t sv[64];
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(ts, r0);
+        tmem_ld_32x32(ts + 32, r1);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float v = (diag && (c * 32 + i) > row) ? -INFINITY : __uint_as_float(r[i]);
-          mx = fmaxf(mx, v);
-        }
+        for (int i = 0; i < 32; ++i) { sv[i] = r0[i]; sv[32 + i] = r1[i]; }
       }
+      tc_fence_before();
+      mbar_arrive(&bars->s_empty[s]);            // the scores live in registers from here on
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float v = (diag && (wg * 64 + i) > row) ? -INFINITY : __uint_as_float(sv[i]);
+        mx = fmaxf(mx, v);
+      }
+      xbuf[(s * 2 + wg) * 128 + row] = mx;
+      mbar_arrive(&bars->mx_full[s]);
+      if (!mbar_wait(&bars->mx_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+      mx = fmaxf(mx, xbuf[(s * 2 + (wg ^ 1)) * 128 + row]);
       const float m_new = fmaxf(m_run, mx);
       const float alpha = fast_exp2((m_run - m_new) * scale_log2);
       const float msc = m_new * scale_log2;
       if (j > 0 && !mbar_wait(&bars->p_empty, (j - 1) & 1, status)) { ok = false; break; }
       float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(ts + c * 32, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(__uint_as_float(r[2 * i]) * scale_log2 - msc);
-          float p1 = fast_exp2(__uint_as_float(r[2 * i + 1]) * scale_log2 - msc);
-          if (diag && (c * 32 + 2 * i) > row) p0 = 0.f;
-          if (diag && (c * 32 + 2 * i + 1) > row) p1 = 0.f;
+          float p0 = fast_exp2(__uint_as_float(sv[c * 32 + 2 * i]) * scale_log2 - msc);
+          float p1 = fast_exp2(__uint_as_float(sv[c * 32 + 2 * i + 1]) * scale_log2 - msc);
+          if (diag && (wg * 64 + c * 32 + 2 * i) > row) p0 = 0.f;
+          if (diag && (wg * 64 + c * 32 + 2 * i + 1) > row) p1 = 0.f;
           rs += p0 + p1;
           w[i] = pack_bf16x2(p0, p1);
         }
-        store_row_chunk_sw128(smem + L::P_OFF + (c / 2) * 16384, row, (c % 2) * 4, w);
+        store_row_chunk_sw128(smem + L::P_OFF + wg * 16384, row, c * 4, w);
       }
-      tc_fence_before();
-      mbar_arrive(&bars->s_empty[s]);
       fence_proxy_async_smem();
       mbar_arrive(&bars->p_full);
       if (j > 0) {
         const int sb = (j - 1) & 1;
         if (!mbar_wait(&bars->o_full[sb], ((j - 1) >> 1) & 1, status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t to = tmem_o + lane_sel + sb * HD;
+        const uint32_t to = tmem_o + lane_sel + sb * HD + wg * HH;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HH / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(to + c * 32, r);
           tmem_ld_wait();
@@ -267,16 +282,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       alpha_prev = alpha;
     }
     if (ok) {
+      // total row sum = this group's partial + the other group's
+      xbuf[(4 + wg) * 128 + row] = l_run;
+      mbar_arrive(&bars->l_full);
+      ok = mbar_wait(&bars->l_full, 0, status);
+    }
+    if (ok) {
+      const float l_tot = l_run + xbuf[(4 + (wg ^ 1)) * 128 + row];
       const int jj = n_blocks - 1;
       const int sb = jj & 1;
       if (mbar_wait(&bars->o_full[sb], (jj >> 1) & 1, status)) {
         tc_fence_after();
-        const uint32_t to = tmem_o + lane_sel + sb * HD;
-        const float inv = 1.f / l_run;
+        const uint32_t to = tmem_o + lane_sel + sb * HD + wg * HH;
+        const float inv = 1.f / l_tot;
         const long long tok = tok0 + static_cast<long long>(qblk) * 128 + row;
-        __nv_bfloat16* orow = out + tok * (static_cast<long long>(Hq) * HD) + head * HD;
+        __nv_bfloat16* orow = out + tok * (static_cast<long long>(Hq) * HD) + head * HD + wg * HH;
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < HH / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(to + c * 32, r);
           tmem_ld_wait();
@@ -294,8 +316,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
             reinterpret_cast<uint4*>(orow + c * 32)[v] = o;
           }
         }
-        lse[(static_cast<long long>(b) * Hq + head) * S + qblk * 128 + row] =
-            m_run * (scale_log2 * 0.6931471805599453f) + logf(l_run);
+        if (wg == 0)
+          lse[(static_cast<long long>(b) * Hq + head) * S + qblk * 128 + row] =
+              m_run * (scale_log2 * 0.6931471805599453f) + logf(l_tot);
       }
     }
   }

@@ -1,16 +1,24 @@
 // Symmetric memory for the fused collective kernels: device allocations that
 // every rank of a group maps into its own address space.
 //
-// A buffer is a plain cudaMalloc allocation (one allocation per buffer, so
-// its IPC handle has offset zero), exported with cudaIpcGetMemHandle; the
-// 64-byte handles travel through the job's torch.distributed store and each
-// peer maps them with cudaIpcOpenMemHandle, which also enables NVLink peer
-// access.  Kernels then use ordinary loads and stores on the peer pointers.
+// A buffer is a plain cudaMalloc allocation exported with cudaIpcGetMemHandle.
+// The runtime may carve several small allocations out of one underlying
+// block, and an IPC handle always names the whole block, so an exported
+// record is (64-byte handle, offset of the buffer inside its block), and the
+// importing side opens each block once per process (reference-counted) and
+// adds the offset.  The records travel through the job's torch.distributed
+// store; cudaIpcOpenMemHandle also enables NVLink peer access.  Kernels then
+// use ordinary loads and stores on the peer pointers.
 #include <ATen/ATen.h>
 #include <cuda_runtime.h>
 #include <torch/library.h>
 
+#include <cuda.h>
+
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
 
 namespace {
 
@@ -33,27 +41,82 @@ Tensor symm_alloc(int64_t nbytes) {
   return at::from_blob(p, {nbytes}, [](void* q) { cudaFree(q); }, opts);
 }
 
-// 64-byte IPC handle of a buffer returned by symm_alloc, as a CPU uint8 tensor.
+using AddressRangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+
+AddressRangeFn address_range_fn() {
+  static AddressRangeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cuda_check(cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q), "cudaGetDriverEntryPoint");
+    TORCH_CHECK(q == cudaDriverEntryPointSuccess && p != nullptr, "symmetric memory: cuMemGetAddressRange unavailable");
+    fn = reinterpret_cast<AddressRangeFn>(p);
+  }
+  return fn;
+}
+
+constexpr int64_t kRecordBytes = static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)) + 8;
+
+// Export record of a buffer returned by symm_alloc: IPC handle of its block + offset inside the block,
+// as a CPU uint8 tensor.
 Tensor symm_export(const Tensor& buf) {
   cudaIpcMemHandle_t h;
   cuda_check(cudaIpcGetMemHandle(&h, buf.data_ptr()), "cudaIpcGetMemHandle");
-  Tensor out = at::empty({static_cast<int64_t>(sizeof(h))}, at::kByte);
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  const CUdeviceptr ptr = reinterpret_cast<CUdeviceptr>(buf.data_ptr());
+  TORCH_CHECK(address_range_fn()(&base, &size, ptr) == CUDA_SUCCESS, "symmetric memory: cuMemGetAddressRange failed");
+  const uint64_t offset = static_cast<uint64_t>(ptr - base);
+  Tensor out = at::empty({kRecordBytes}, at::kByte);
   std::memcpy(out.data_ptr(), &h, sizeof(h));
+  std::memcpy(static_cast<uint8_t*>(out.data_ptr()) + sizeof(h), &offset, 8);
   return out;
 }
 
+struct OpenedBlock {
+  void* base = nullptr;
+  int refs = 0;
+};
+std::mutex g_mu;
+std::map<std::string, OpenedBlock> g_blocks;          // handle bytes -> mapping of that block in this process
+std::multimap<int64_t, std::string> g_ptr_block;      // address handed out -> its block
+
 // Maps a peer's buffer; returns the device address in this process.
-int64_t symm_import(const Tensor& handle) {
-  TORCH_CHECK(handle.numel() == static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)), "bad IPC handle size");
+int64_t symm_import(const Tensor& record) {
+  TORCH_CHECK(record.numel() == kRecordBytes, "bad symmetric-memory export record");
   cudaIpcMemHandle_t h;
-  std::memcpy(&h, handle.data_ptr(), sizeof(h));
-  void* p = nullptr;
-  cuda_check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
-  return reinterpret_cast<int64_t>(p);
+  uint64_t offset = 0;
+  std::memcpy(&h, record.data_ptr(), sizeof(h));
+  std::memcpy(&offset, static_cast<const uint8_t*>(record.data_ptr()) + sizeof(h), 8);
+  const std::string key(reinterpret_cast<const char*>(&h), sizeof(h));
+  std::lock_guard<std::mutex> lock(g_mu);
+  OpenedBlock& blk = g_blocks[key];
+  if (blk.refs == 0) {
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      g_blocks.erase(key);
+      cuda_check(e, "cudaIpcOpenMemHandle");
+    }
+    blk.base = p;
+  }
+  ++blk.refs;
+  const int64_t addr = reinterpret_cast<int64_t>(static_cast<uint8_t*>(blk.base) + offset);
+  g_ptr_block.emplace(addr, key);
+  return addr;
 }
 
 void symm_release(int64_t ptr) {
-  if (ptr != 0) cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr));
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = g_ptr_block.find(ptr);
+  if (it == g_ptr_block.end()) return;
+  auto blk = g_blocks.find(it->second);
+  g_ptr_block.erase(it);
+  if (blk == g_blocks.end()) return;
+  if (--blk->second.refs == 0) {
+    cudaIpcCloseMemHandle(blk->second.base);
+    g_blocks.erase(blk);
+  }
 }
 
 }  // namespace

@@ -165,6 +165,10 @@ def piper_setup(model_class, model_args=(), model_kwargs: Optional[dict] = None,
     if len(per_device) != layout.pp_degree:
         raise RuntimeError(f"compiled {len(per_device)} per-device DAGs for {layout.pp_degree} pipeline ranks")
     channels = assign_pipeline_channels(global_dag, per_device, layout.device_tuples)
+    if os.environ.get("PIPER_CHECK_PLANS", "1") != "0":
+        # dispatch order, channel FIFO pairing and cross-rank deadlock freedom, checked on the host before launch
+        from .compiler.check import check_plans
+        check_plans(per_device)
 
     groups = None
     if backend is not None:

@@ -52,7 +52,15 @@ class SymmetricBuffer:
         return self.peer_ptrs + int(offset_bytes)
 
     def close(self) -> None:
-        lib = native.lib()
-        for p in self._imported:
-            lib.symm_release(p)
-        self._imported = []
+        """Unmaps the peers' buffers (the local allocation is freed with the object)."""
+        imported, self._imported = self._imported, []
+        if imported:
+            lib = native.lib()
+            for p in imported:
+                lib.symm_release(p)
+
+    def __del__(self) -> None:
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -340,3 +340,62 @@ def test_fx_json_roundtrip_of_traced_segments():
             prev = clone(*args)
     out = prev[0] if isinstance(prev, (tuple, list)) else prev
     assert torch.allclose(out, ref, atol=1e-5)
+
+
+# ------------------------------------------------------------------ plan checker
+def _plan(nodes, edges):
+    """nodes: (uid, kind, stream, meta); edges: (src, dst, dep_kind)."""
+    dag = TrainingDAG()
+    for uid, kind, stream, meta in nodes:
+        dag.add_node(TrainingDAGNode(uid=uid, node_kind=kind, compute_subkind="FWD" if kind == "COMPUTE" else None,
+                                     tag={}, device=[0], stream=stream, node_meta=dict(meta)))
+    for s, d, k in edges:
+        dag.add_edge(TrainingDAGEdge(s, d, k))
+    return dag
+
+
+def test_plan_checker_accepts_compiled_schedules_and_finds_defects():
+    from piper_b200.compiler.check import PlanError, check_plans
+    from piper_b200.engine import assign_pipeline_channels
+
+    gm, _, _ = _capture(_TwoStage(), torch.randn(2, 8))
+    for order_rows in (build_1f1b_schedule(2, 4), build_zerobubble_schedule(2, 4)):
+        directives = [
+            {"op": "place", "filter": {"PP": 0}, "devices": [0], "stream": "pp_stream"},
+            {"op": "place", "filter": {"PP": 1}, "devices": [1], "stream": "pp_stream"},
+            {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 4},
+            *order_rows,
+        ]
+        dag, per_dev, _ = compile_training_dags(gm, directives)
+        assign_pipeline_channels(dag, per_dev, [(0,), (1,)])
+        stats = check_plans(per_dev)
+        assert stats["ranks"] == 2 and stats["messages"] == 8
+    # swapped receives of one channel on rank 1: messages would be delivered to the wrong microbatch
+    order1 = serial_topological_order(per_dev[1])
+    recvs = [u for u in order1 if per_dev[1].nodes[u].node_kind == "RECV_COMM"
+             and per_dev[1].nodes[u].node_meta["channel_base"][4] == per_dev[1].nodes[
+                 next(v for v in order1 if per_dev[1].nodes[v].node_kind == "RECV_COMM")].node_meta["channel_base"][4]]
+    i, j = order1.index(recvs[0]), order1.index(recvs[1])
+    swapped = list(order1)
+    swapped[i], swapped[j] = swapped[j], swapped[i]
+    with pytest.raises(PlanError):
+        check_plans(per_dev, [serial_topological_order(per_dev[0]), swapped])
+
+    # hand-built deadlock: each rank queues, on its compute stream, the consumer of the peer's message in front of
+    # the producer of its own message
+    ch_a, ch_b = ((0,), (1,), 0, 1, "F"), ((1,), (0,), 1, 0, "F")
+    r0 = _plan([("x0", "COMPUTE", "default_stream", {}), ("f0", "COMPUTE", "default_stream", {}),
+                ("send_a", "SEND_COMM", "pp", {"channel_base": ch_a, "pair_uid": "recv_a"}),
+                ("recv_b", "RECV_COMM", "pp", {"channel_base": ch_b})],
+               [("f0", "send_a", "data"), ("recv_b", "x0", "data")])
+    r1 = _plan([("x1", "COMPUTE", "default_stream", {}), ("f1", "COMPUTE", "default_stream", {}),
+                ("send_b", "SEND_COMM", "pp", {"channel_base": ch_b, "pair_uid": "recv_b"}),
+                ("recv_a", "RECV_COMM", "pp", {"channel_base": ch_a})],
+               [("f1", "send_b", "data"), ("recv_a", "x1", "data")])
+    good = [["f0", "send_a", "recv_b", "x0"], ["f1", "send_b", "recv_a", "x1"]]
+    assert check_plans([r0, r1], good)["messages"] == 2
+    bad = [["recv_b", "x0", "f0", "send_a"], ["recv_a", "x1", "f1", "send_b"]]
+    with pytest.raises(PlanError, match="deadlock"):
+        check_plans([r0, r1], bad)
+    with pytest.raises(PlanError, match="dispatched before"):
+        check_plans([r0, r1], [["send_a", "f0", "recv_b", "x0"], good[1]])

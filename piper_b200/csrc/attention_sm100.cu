@@ -363,10 +363,10 @@ struct BwdSmem {
   static constexpr int X1_OFF = 0;
   static constexpr int X2_OFF = X_TILE;
   static constexpr int Y_OFF = 2 * X_TILE;         // 2 stages x (Y1, Y2)
-  static constexpr int P_OFF = Y_OFF + 4 * Y_TILE;
-  static constexpr int DS_OFF = P_OFF + PT_BYTES;
-  static constexpr int VEC_OFF = DS_OFF + PT_BYTES;  // 2 stages x (lse[64], delta[64]) floats
-  static constexpr int BAR_OFF = VEC_OFF + 2 * 2 * 64 * 4;
+  static constexpr int P_OFF = Y_OFF + 4 * Y_TILE;       // 2 buffers
+  static constexpr int DS_OFF = P_OFF + 2 * PT_BYTES;    // 2 buffers
+  static constexpr int VEC_OFF = DS_OFF + 2 * PT_BYTES;  // 4 stages x (lse[64], delta[64]) floats
+  static constexpr int BAR_OFF = VEC_OFF + 4 * 2 * 64 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -374,7 +374,7 @@ struct BwdBars {
   uint64_t x_full;
   uint64_t y_full[2], y_empty[2];
   uint64_t s_full[2], s_empty[2];     // S' and dP' pair
-  uint64_t t_full, t_empty;           // P'/dS' shared-memory tiles
+  uint64_t t_full[2], t_empty[2];     // P'/dS' shared-memory tiles (double-buffered)
   uint64_t v_full[2];                 // per-column lse/delta vectors (MODE 1)
   uint64_t acc_full;
   uint32_t tmem_base;
@@ -422,8 +422,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       mbar_init(&bars->s_empty[i], 256);
       mbar_init(&bars->v_full[i], 64);
     }
-    mbar_init(&bars->t_full, 256);
-    mbar_init(&bars->t_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->t_full[i], 256);
+      mbar_init(&bars->t_empty[i], 1);
+    }
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_qkv_x);
@@ -525,25 +527,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         if (it >= 1) {
           const int jt = it - 1;
           const int st = jt & 1;
-          if (!mbar_wait(&bars->t_full, jt & 1, status)) { ok = false; break; }
+          if (!mbar_wait(&bars->t_full[st], (jt >> 1) & 1, status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
           const uint32_t y2 = y1 + L::Y_TILE;
+          const uint32_t ds_t = ds_addr + st * L::PT_BYTES;
+          const uint32_t p_t = p_addr + st * L::PT_BYTES;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {   // contraction over the 64 streamed rows
-            umma_bf16_ss(tmem_acc1, umma_desc_sw128(ds_addr + ks * 32, 16, 1024),
+            umma_bf16_ss(tmem_acc1, umma_desc_sw128(ds_t + ks * 32, 16, 1024),
                          umma_desc_sw128(y1 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
                          (jt > 0 || ks > 0) ? 1u : 0u);
           }
           if (MODE == 1) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_bf16_ss(tmem_acc2, umma_desc_sw128(p_addr + ks * 32, 16, 1024),
+              umma_bf16_ss(tmem_acc2, umma_desc_sw128(p_t + ks * 32, 16, 1024),
                            umma_desc_sw128(y2 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
                            (jt > 0 || ks > 0) ? 1u : 0u);
             }
           }
-          umma_commit(&bars->t_empty);
+          umma_commit(&bars->t_empty[st]);
           umma_commit(&bars->y_empty[st]);
           if (jt == n_iter - 1) umma_commit(&bars->acc_full);
         }
@@ -565,14 +569,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
+      // lse/delta vectors: four stages, so a stage is rewritten only after every thread has left the
+      // iteration that read it (a thread enters iteration it only after the MMAs of it - 3 have retired)
+      const int vs = it & 3;
       const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;
       if (MODE == 1) {
         // Per-column lse/delta of the streamed query tile -> shared memory.
         const int hh = g * group + it / tiles_per_head;
         if (wg == 0 && row < 64) {
           const long long idx = (static_cast<long long>(b) * Hq + hh) * S + ti * 64 + row;
-          vec[st * 128 + row] = lse[idx] * 1.4426950408889634f;
-          vec[st * 128 + 64 + row] = delta[idx];
+          vec[vs * 128 + row] = lse[idx] * 1.4426950408889634f;
+          vec[vs * 128 + 64 + row] = delta[idx];
           mbar_arrive(&bars->v_full[st]);
         }
         // Bounded wait instead of a named barrier: a thread that gave up on
@@ -581,7 +588,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       }
       if (!mbar_wait(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       tc_fence_after();
-      if (it > 0 && !mbar_wait(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
       // Causal mask is needed only where the streamed tile overlaps the
       // stationary rows: element (x row, y col) is kept iff key <= query.
       const int ypos0 = ti * 64;
@@ -593,6 +599,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         tmem_ld_32x32(ts + c * 32, sv);
         tmem_ld_32x32(ts + 64 + c * 32, dv);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->s_empty[st]);   // S'/dP' of this stage now live in registers
         uint32_t pw[16], dw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -600,8 +608,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int col = c * 32 + 2 * i + e;
-            const float l2 = (MODE == 0) ? row_lse : vec[st * 128 + col];
-            const float dl = (MODE == 0) ? row_delta : vec[st * 128 + 64 + col];
+            const float l2 = (MODE == 0) ? row_lse : vec[vs * 128 + col];
+            const float dl = (MODE == 0) ? row_delta : vec[vs * 128 + 64 + col];
             float pv = fast_exp2(__uint_as_float(sv[2 * i + e]) * scale_log2 - l2);
             if (need_mask) {
               const int qpos = (MODE == 0) ? xpos : ypos0 + col;
@@ -614,13 +622,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           pw[i] = pack_bf16x2(p[0], p[1]);
           dw[i] = pack_bf16x2(d[0], d[1]);
         }
-        if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
-        store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
+        // the tile buffer of this parity was last read by the MMAs of iteration it - 2
+        if (it >= 2 && !mbar_wait(&bars->t_empty[st], ((it >> 1) & 1) ^ 1, status)) { ok = false; break; }
+        if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF + st * L::PT_BYTES, row, c * 4, pw);
+        store_row_chunk_sw128(smem + L::DS_OFF + st * L::PT_BYTES, row, c * 4, dw);
       }
-      tc_fence_before();
-      mbar_arrive(&bars->s_empty[st]);
       fence_proxy_async_smem();
-      mbar_arrive(&bars->t_full);
+      mbar_arrive(&bars->t_full[st]);
     }
     if (ok && mbar_wait(&bars->acc_full, 0, status)) {
       tc_fence_after();

@@ -399,9 +399,25 @@ int f1_rs_adam_ag(const float* const* peer_grads, void* const* peer_params, uint
   if (shard_numel % 4 != 0 || dp < 1) return -1;
   if (shard_numel == 0) return 0;
   auto pp = reinterpret_cast<__nv_bfloat16* const*>(peer_params);
+  // Every CTA waits inside the kernel for the last CTA of each rank, so the whole grid has to be resident at
+  // once: never launch more CTAs than fit on the device.
 #define PIPER_F1_LAUNCH(DPV)                                                                                   \
-  f1_kernel<DPV><<<num_ctas, F1_THREADS, 0, st>>>(peer_grads, pp, peer_flags, master, m, v, my_rank, dp,        \
-                                                  shard_numel, epoch, h, cta_counter, status, timeout_ns)
+  {                                                                                                            \
+    static int capacity = 0;                                                                                   \
+    if (capacity == 0) {                                                                                       \
+      int per_sm = 0, dev = 0, sms = 0;                                                                        \
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, f1_kernel<DPV>, F1_THREADS, 0) !=             \
+              cudaSuccess ||                                                                                   \
+          cudaGetDevice(&dev) != cudaSuccess ||                                                                \
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || per_sm < 1)      \
+        return -2;                                                                                             \
+      capacity = per_sm * sms;                                                                                 \
+    }                                                                                                          \
+    if (num_ctas > capacity) num_ctas = capacity;                                                              \
+    if (num_ctas < 1) num_ctas = 1;                                                                            \
+    f1_kernel<DPV><<<num_ctas, F1_THREADS, 0, st>>>(peer_grads, pp, peer_flags, master, m, v, my_rank, dp,      \
+                                                    shard_numel, epoch, h, cta_counter, status, timeout_ns);   \
+  }
   switch (dp) {
     case 1: PIPER_F1_LAUNCH(1); break;
     case 2: PIPER_F1_LAUNCH(2); break;

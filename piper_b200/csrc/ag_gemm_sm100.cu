@@ -324,7 +324,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               reinterpret_cast<uint4*>(crow)[v] = o;
             }
           } else {
-            for (int j = 0; j < 32 && col0 + j < N; ++j) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+            #pragma unroll
+                for (int j = 0; j < 32; ++j)   // constant indices keep r[] in registers
+                  if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
           }
         }
       }

@@ -74,7 +74,8 @@ struct FwdSmem {
 
 struct FwdBars {
   uint64_t q_full;
-  uint64_t kv_full[2], kv_empty[2];
+  uint64_t k_full[2], k_empty[2];     // K is free again once S = Q K^T of its block has been computed ...
+  uint64_t v_full[2], v_empty[2];     // ... V only after P V, so the two rings run at different distances
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full, p_empty;
   uint64_t o_full[2], o_empty[2];
@@ -103,8 +104,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->kv_full[i], 1);
-      mbar_init(&bars->kv_empty[i], 1);
+      mbar_init(&bars->k_full[i], 1);
+      mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1);
+      mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->s_empty[i], 256);
       mbar_init(&bars->o_full[i], 1);
@@ -135,24 +138,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       for (int h = 0; h < L::HALVES; ++h)
         tma_load_2d(smem + L::Q_OFF + h * 16384, &tmap, &bars->q_full, head * HD + 64 * h,
                     static_cast<int>(tok0) + qblk * 128);
-      int j = 0;
-      for (; j < n_blocks; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&bars->kv_empty[s], ((j >> 1) & 1) ^ 1, status)) break;
-        mbar_arrive_expect_tx(&bars->kv_full[s], 2 * L::TILE);
-        for (int h = 0; h < L::HALVES; ++h) {
-          tma_load_2d(smem + L::K_OFF + s * L::TILE + h * 16384, &tmap, &bars->kv_full[s],
-                      (Hq + g) * HD + 64 * h, static_cast<int>(tok0) + j * 128);
-          tma_load_2d(smem + L::V_OFF + s * L::TILE + h * 16384, &tmap, &bars->kv_full[s],
-                      (Hq + Hkv + g) * HD + 64 * h, static_cast<int>(tok0) + j * 128);
+      // K and V blocks are loaded as soon as their own stage is free, whichever comes first
+      int kj = 0, vj = 0;
+      uint32_t idle = 0;
+      bool ok = true;
+      while ((kj < n_blocks || vj < n_blocks) && ok) {
+        bool progressed = false;
+        if (kj < n_blocks && mbar_test_wait(&bars->k_empty[kj & 1], ((kj >> 1) & 1) ^ 1)) {
+          const int s = kj & 1;
+          mbar_arrive_expect_tx(&bars->k_full[s], L::TILE);
+          for (int h = 0; h < L::HALVES; ++h)
+            tma_load_2d(smem + L::K_OFF + s * L::TILE + h * 16384, &tmap, &bars->k_full[s],
+                        (Hq + g) * HD + 64 * h, static_cast<int>(tok0) + kj * 128);
+          ++kj;
+          progressed = true;
+        }
+        if (vj < n_blocks && mbar_test_wait(&bars->v_empty[vj & 1], ((vj >> 1) & 1) ^ 1)) {
+          const int s = vj & 1;
+          mbar_arrive_expect_tx(&bars->v_full[s], L::TILE);
+          for (int h = 0; h < L::HALVES; ++h)
+            tma_load_2d(smem + L::V_OFF + s * L::TILE + h * 16384, &tmap, &bars->v_full[s],
+                        (Hq + Hkv + g) * HD + 64 * h, static_cast<int>(tok0) + vj * 128);
+          ++vj;
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else if (++idle > kMaxMbarPolls) {
+          atomicCAS(status, 0, kStatusMbarTimeout);
+          ok = false;
+        } else if ((idle & 1023u) == 0 && *reinterpret_cast<volatile int*>(status) != 0) {
+          ok = false;
         }
       }
-      if (j < n_blocks) {
+      if (!ok) {
         // Unwinding after a failed wait: let the copies already issued land
         // before the CTA and its shared memory go away.
         mbar_wait(&bars->q_full, 0, nullptr);
-        for (int jj = j - 1; jj >= 0 && jj >= j - 2; --jj)
-          mbar_wait(&bars->kv_full[jj & 1], (jj >> 1) & 1, nullptr);
+        for (int jj = kj - 1; jj >= 0 && jj >= kj - 2; --jj)
+          mbar_wait(&bars->k_full[jj & 1], (jj >> 1) & 1, nullptr);
+        for (int jj = vj - 1; jj >= 0 && jj >= vj - 2; --jj)
+          mbar_wait(&bars->v_full[jj & 1], (jj >> 1) & 1, nullptr);
       }
     }
   } else if (warp == 5) {
@@ -163,38 +189,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
       bool ok = mbar_wait(&bars->q_full, 0, status);
-      for (int j = 0; j <= n_blocks && ok; ++j) {
-        if (j < n_blocks) {
-          const int s = j & 1;
-          if (!mbar_wait(&bars->kv_full[s], (j >> 1) & 1, status)) { ok = false; break; }
-          if (!mbar_wait(&bars->s_empty[s], ((j >> 1) & 1) ^ 1, status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(smem + L::K_OFF + s * L::TILE);
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-            umma_bf16_ss(tmem_s + s * 128, umma_desc_sw128(q_addr + off, 16, 1024),
-                         umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
-          }
-          umma_commit(&bars->s_full[s]);
-        }
-        if (j >= 1) {
-          const int jj = j - 1;
+      // Two queues served in whatever order their inputs arrive: S of block s_next (needs K and a free TMEM
+      // stage) and P V of block p_next (needs the probabilities, V and a free output stage).
+      int s_next = 0, p_next = 0;
+      uint32_t idle = 0;
+      while (p_next < n_blocks && ok) {
+        bool progressed = false;
+        if (p_next < s_next) {
+          const int jj = p_next;
           const int sb = jj & 1;
-          if (!mbar_wait(&bars->p_full, jj & 1, status)) { ok = false; break; }
-          if (!mbar_wait(&bars->o_empty[sb], ((jj >> 1) & 1) ^ 1, status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(smem + L::V_OFF + sb * L::TILE);
+          if (mbar_test_wait(&bars->p_full, jj & 1) && mbar_test_wait(&bars->v_full[sb], (jj >> 1) & 1) &&
+              mbar_test_wait(&bars->o_empty[sb], ((jj >> 1) & 1) ^ 1)) {
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(smem + L::V_OFF + sb * L::TILE);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
-            umma_bf16_ss(tmem_o + sb * HD, umma_desc_sw128(p_addr + a_off, 16, 1024),
-                         umma_desc_sw128(v_addr + ks * 2048, 16384, 1024), idesc_pv,
-                         ks > 0 ? 1u : 0u);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
+              umma_bf16_ss(tmem_o + sb * HD, umma_desc_sw128(p_addr + a_off, 16, 1024),
+                           umma_desc_sw128(v_addr + ks * 2048, 16384, 1024), idesc_pv,
+                           ks > 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->p_empty);
+            umma_commit(&bars->o_full[sb]);
+            umma_commit(&bars->v_empty[sb]);
+            ++p_next;
+            progressed = true;
           }
-          umma_commit(&bars->p_empty);
-          umma_commit(&bars->o_full[sb]);
-          umma_commit(&bars->kv_empty[sb]);
+        }
+        if (s_next < n_blocks) {
+          const int j = s_next;
+          const int s = j & 1;
+          if (mbar_test_wait(&bars->k_full[s], (j >> 1) & 1) &&
+              mbar_test_wait(&bars->s_empty[s], ((j >> 1) & 1) ^ 1)) {
+            tc_fence_after();
+            const uint32_t k_addr = smem_u32(smem + L::K_OFF + s * L::TILE);
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+              umma_bf16_ss(tmem_s + s * 128, umma_desc_sw128(q_addr + off, 16, 1024),
+                           umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->s_full[s]);
+            umma_commit(&bars->k_empty[s]);
+            ++s_next;
+            progressed = true;
+          }
+        }
+        if (progressed) {
+          idle = 0;
+        } else if (++idle > kMaxMbarPolls) {
+          atomicCAS(status, 0, kStatusMbarTimeout);
+          ok = false;
+        } else if ((idle & 1023u) == 0 && *reinterpret_cast<volatile int*>(status) != 0) {
+          ok = false;
         }
       }
     }
@@ -362,19 +409,20 @@ struct BwdSmem {
   static constexpr int PT_BYTES = 128 * 64 * 2;    // P' or dS' tile (one swizzle row per row)
   static constexpr int X1_OFF = 0;
   static constexpr int X2_OFF = X_TILE;
-  static constexpr int Y_OFF = 2 * X_TILE;         // 2 stages x (Y1, Y2)
-  static constexpr int P_OFF = Y_OFF + 4 * Y_TILE;       // 2 buffers
-  static constexpr int DS_OFF = P_OFF + 2 * PT_BYTES;    // 2 buffers
-  static constexpr int VEC_OFF = DS_OFF + 2 * PT_BYTES;  // 4 stages x (lse[64], delta[64]) floats
+  static constexpr int Y_STAGES = 3;
+  static constexpr int Y_OFF = 2 * X_TILE;         // Y_STAGES x (Y1, Y2)
+  static constexpr int P_OFF = Y_OFF + Y_STAGES * 2 * Y_TILE;
+  static constexpr int DS_OFF = P_OFF + PT_BYTES;
+  static constexpr int VEC_OFF = DS_OFF + PT_BYTES;      // 4 stages x (lse[64], delta[64]) floats
   static constexpr int BAR_OFF = VEC_OFF + 4 * 2 * 64 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
 struct BwdBars {
   uint64_t x_full;
-  uint64_t y_full[2], y_empty[2];
+  uint64_t y_full[3], y_empty[3];     // streamed tiles (BwdSmem::Y_STAGES)
   uint64_t s_full[2], s_empty[2];     // S' and dP' pair
-  uint64_t t_full[2], t_empty[2];     // P'/dS' shared-memory tiles (double-buffered)
+  uint64_t t_full, t_empty;           // P'/dS' shared-memory tiles
   uint64_t v_full[2];                 // per-column lse/delta vectors (MODE 1)
   uint64_t acc_full;
   uint32_t tmem_base;
@@ -415,17 +463,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->x_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < L::Y_STAGES; ++i) {
       mbar_init(&bars->y_full[i], 1);
       mbar_init(&bars->y_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->s_empty[i], 256);
       mbar_init(&bars->v_full[i], 64);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->t_full[i], 256);
-      mbar_init(&bars->t_empty[i], 1);
-    }
+    mbar_init(&bars->t_full, 256);
+    mbar_init(&bars->t_empty, 1);
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_qkv_x);
@@ -464,8 +512,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       }
       int it = 0;
       for (; it < n_iter; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&bars->y_empty[st], ((it >> 1) & 1) ^ 1, status)) break;
+        const int st = it % L::Y_STAGES;
+        if (!mbar_wait(&bars->y_empty[st], ((it / L::Y_STAGES) & 1) ^ 1, status)) break;
         const int hh = (MODE == 0) ? hy : g * group + it / tiles_per_head;   // query head
         const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;      // streamed tile index
         const int yrow = static_cast<int>(tok0) + ti * 64;
@@ -486,8 +534,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       if (it < n_iter) {
         // Unwinding: wait (bounded) for the copies in flight.
         mbar_wait(&bars->x_full, 0, nullptr);
-        for (int jj = it - 1; jj >= 0 && jj >= it - 2; --jj)
-          mbar_wait(&bars->y_full[jj & 1], (jj >> 1) & 1, nullptr);
+        for (int jj = it - 1; jj >= 0 && jj > it - 1 - L::Y_STAGES; --jj)
+          mbar_wait(&bars->y_full[jj % L::Y_STAGES], (jj / L::Y_STAGES) & 1, nullptr);
       }
     }
   } else if (warp == 5) {
@@ -500,56 +548,75 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
       const uint32_t ds_addr = smem_u32(smem + L::DS_OFF);
       bool ok = mbar_wait(&bars->x_full, 0, status);
-      for (int it = 0; it <= n_iter && ok; ++it) {
-        if (it < n_iter) {
-          const int st = it & 1;
-          if (!mbar_wait(&bars->y_full[st], (it >> 1) & 1, status)) { ok = false; break; }
-          if (!mbar_wait(&bars->s_empty[st], ((it >> 1) & 1) ^ 1, status)) { ok = false; break; }
+      // Two queues served in whatever order their inputs arrive: S'/dP' of tile s_next needs its streamed tile
+      // and a free TMEM stage; the accumulation of tile a_next needs the P'/dS' tiles the threads wrote.  A fixed
+      // order would let a streamed tile that is still in flight hold back the accumulation that frees the
+      // shared-memory stage the next load is waiting for.
+      int s_next = 0, a_next = 0;
+      uint32_t idle = 0;
+      while (a_next < n_iter && ok) {
+        bool progressed = false;
+        if (a_next < s_next && mbar_test_wait(&bars->t_full, a_next & 1)) {
+          const int jt = a_next;
+          const int st = jt % L::Y_STAGES;
           tc_fence_after();
           const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
           const uint32_t y2 = y1 + L::Y_TILE;
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
-            const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
-            umma_bf16_ss(tmem_base + st * 128, umma_desc_sw128(x1 + xo, 16, 1024),
-                         umma_desc_sw128(y1 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-          }
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks) {
-            const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
-            const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
-            umma_bf16_ss(tmem_base + st * 128 + 64, umma_desc_sw128(x2 + xo, 16, 1024),
-                         umma_desc_sw128(y2 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-          }
-          umma_commit(&bars->s_full[st]);
-        }
-        if (it >= 1) {
-          const int jt = it - 1;
-          const int st = jt & 1;
-          if (!mbar_wait(&bars->t_full[st], (jt >> 1) & 1, status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
-          const uint32_t y2 = y1 + L::Y_TILE;
-          const uint32_t ds_t = ds_addr + st * L::PT_BYTES;
-          const uint32_t p_t = p_addr + st * L::PT_BYTES;
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {   // contraction over the 64 streamed rows
-            umma_bf16_ss(tmem_acc1, umma_desc_sw128(ds_t + ks * 32, 16, 1024),
+            umma_bf16_ss(tmem_acc1, umma_desc_sw128(ds_addr + ks * 32, 16, 1024),
                          umma_desc_sw128(y1 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
                          (jt > 0 || ks > 0) ? 1u : 0u);
           }
           if (MODE == 1) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_bf16_ss(tmem_acc2, umma_desc_sw128(p_t + ks * 32, 16, 1024),
+              umma_bf16_ss(tmem_acc2, umma_desc_sw128(p_addr + ks * 32, 16, 1024),
                            umma_desc_sw128(y2 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
                            (jt > 0 || ks > 0) ? 1u : 0u);
             }
           }
-          umma_commit(&bars->t_empty[st]);
+          umma_commit(&bars->t_empty);
           umma_commit(&bars->y_empty[st]);
           if (jt == n_iter - 1) umma_commit(&bars->acc_full);
+          ++a_next;
+          progressed = true;
+        }
+        if (s_next < n_iter) {
+          const int it = s_next;
+          const int st = it % L::Y_STAGES;
+          const int ss = it & 1;
+          if (mbar_test_wait(&bars->y_full[st], (it / L::Y_STAGES) & 1) &&
+              mbar_test_wait(&bars->s_empty[ss], ((it >> 1) & 1) ^ 1)) {
+            tc_fence_after();
+            const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
+            const uint32_t y2 = y1 + L::Y_TILE;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
+              const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
+              umma_bf16_ss(tmem_base + ss * 128, umma_desc_sw128(x1 + xo, 16, 1024),
+                           umma_desc_sw128(y1 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+            }
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
+              const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
+              umma_bf16_ss(tmem_base + ss * 128 + 64, umma_desc_sw128(x2 + xo, 16, 1024),
+                           umma_desc_sw128(y2 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+            }
+            umma_commit(&bars->s_full[ss]);
+            ++s_next;
+            progressed = true;
+          }
+        }
+        if (progressed) {
+          idle = 0;
+        } else if (++idle > kMaxMbarPolls) {
+          atomicCAS(status, 0, kStatusMbarTimeout);
+          ok = false;
+        } else if ((idle & 1023u) == 0 && *reinterpret_cast<volatile int*>(status) != 0) {
+          ok = false;
         }
       }
     }
@@ -566,21 +633,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       row_lse = lse[idx] * 1.4426950408889634f;
       row_delta = delta[idx];
     }
+    float pre_lse = 0.f, pre_delta = 0.f;      // MODE 1: this thread's lse/delta entries of the next streamed tile
+    if (MODE == 1 && wg == 0 && row < 64 && n_iter > 0) {
+      const long long idx = (static_cast<long long>(b) * Hq + g * group) * S + 2 * xb * 64 + row;
+      pre_lse = lse[idx] * 1.4426950408889634f;
+      pre_delta = delta[idx];
+    }
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
       // lse/delta vectors: four stages, so a stage is rewritten only after every thread has left the
-      // iteration that read it (a thread enters iteration it only after the MMAs of it - 3 have retired)
+      // iteration that read it (a thread enters iteration it only after the MMAs of it - 2 have retired)
       const int vs = it & 3;
       const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;
       if (MODE == 1) {
-        // Per-column lse/delta of the streamed query tile -> shared memory.
-        const int hh = g * group + it / tiles_per_head;
+        // Per-column lse/delta of the streamed query tile -> shared memory.  The values of the next tile are
+        // requested right away and stay in flight while this tile is processed.
         if (wg == 0 && row < 64) {
-          const long long idx = (static_cast<long long>(b) * Hq + hh) * S + ti * 64 + row;
-          vec[vs * 128 + row] = lse[idx] * 1.4426950408889634f;
-          vec[vs * 128 + 64 + row] = delta[idx];
+          vec[vs * 128 + row] = pre_lse;
+          vec[vs * 128 + 64 + row] = pre_delta;
           mbar_arrive(&bars->v_full[st]);
+          if (it + 1 < n_iter) {
+            const int hn = g * group + (it + 1) / tiles_per_head;
+            const int tn = 2 * xb + (it + 1) % tiles_per_head;
+            const long long idx = (static_cast<long long>(b) * Hq + hn) * S + tn * 64 + row;
+            pre_lse = lse[idx] * 1.4426950408889634f;
+            pre_delta = delta[idx];
+          }
         }
         // Bounded wait instead of a named barrier: a thread that gave up on
         // an earlier wait must not strand the others here.
@@ -622,13 +701,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           pw[i] = pack_bf16x2(p[0], p[1]);
           dw[i] = pack_bf16x2(d[0], d[1]);
         }
-        // the tile buffer of this parity was last read by the MMAs of iteration it - 2
-        if (it >= 2 && !mbar_wait(&bars->t_empty[st], ((it >> 1) & 1) ^ 1, status)) { ok = false; break; }
-        if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF + st * L::PT_BYTES, row, c * 4, pw);
-        store_row_chunk_sw128(smem + L::DS_OFF + st * L::PT_BYTES, row, c * 4, dw);
+        // the tiles were last read by the MMAs of the previous iteration
+        if (it >= 1 && !mbar_wait(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
+        if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
+        store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bars->t_full[st]);
+      mbar_arrive(&bars->t_full);
     }
     if (ok && mbar_wait(&bars->acc_full, 0, status)) {
       tc_fence_after();

@@ -57,8 +57,8 @@ float* opt_f32(const OptTensor& t) {
 // C[M,N] = A * B^T.  a: [M,K] (a_mn=false) or [K,M] (a_mn=true); b: [N,K]
 // (b_mn=false) or [K,N] (b_mn=true).  c bf16 -> store; c fp32 -> store or
 // accumulate.
-void gemm(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, bool accumulate,
-          Tensor status) {
+void gemm_tiled(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, bool accumulate, Tensor status,
+                int64_t tile) {
   check_bf16(a, "a");
   check_bf16(b, "b");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm expects 2-D tensors");
@@ -97,7 +97,13 @@ void gemm(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, bool
   }
   g.accumulate = accumulate ? 1 : 0;
   g.status = status.data_ptr<int>();
+  TORCH_CHECK(tile == 0 || tile == 128 || tile == 256, "gemm tile must be 0 (auto), 128 or 256");
+  g.tile = static_cast<int>(tile);
   check_rc(piper::gemm_bf16_launch(g, num_sms(), cur_stream()), "gemm");
+}
+
+void gemm(const Tensor& a, const Tensor& b, Tensor c, bool a_mn, bool b_mn, bool accumulate, Tensor status) {
+  gemm_tiled(a, b, c, a_mn, b_mn, accumulate, status, 0);
 }
 
 void rmsnorm_fwd(const Tensor& x, const OptTensor& res, const Tensor& w, Tensor y, const OptTensor& h_out,
@@ -284,6 +290,7 @@ void attn_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, const Te
 TORCH_LIBRARY(piper_c, m) {
   m.def("kernel_launch_count", &kernel_launch_count);
   m.def("gemm", &gemm);
+  m.def("gemm_tiled", &gemm_tiled);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_num_partials", &rmsnorm_bwd_num_partials);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

@@ -40,7 +40,10 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int MN_BOX_BYTES = 64 * BK * 2;    // one MN-major TMA box: 64 k-rows x 128 B
 constexpr int NUM_THREADS = 256;
+constexpr int C_STAGE_BYTES = 32 * 32 * 4;   // fp32 epilogue: one 32x32 block per warp, two buffers per warp
+constexpr int C_STAGING_BYTES = 4 * 2 * C_STAGE_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES_F32 = STAGES * STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers, padded*/ + C_STAGING_BYTES;
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -55,8 +58,8 @@ struct Barriers {
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            void* __restrict__ c_ptr, long long ldc, int M, int N, int K, int accumulate,
-            int* status, int* sched) {
+            const __grid_constant__ CUtensorMap tmap_c, void* __restrict__ c_ptr, long long ldc, int M, int N,
+            int K, int accumulate, int* status, int* sched) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -236,28 +239,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 reinterpret_cast<uint4*>(crow)[v] = o;
               }
             } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j)
-                crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+              #pragma unroll
+                for (int j = 0; j < 32; ++j)   // constant indices keep r[] in registers
+                  if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
             }
-          } else {
-            float* crow = reinterpret_cast<float*>(c_ptr) + row * ldc + col0;
-            if (col0 + 32 <= N) {
+          }
+        }
+        if (EPI == kEpiAccumF32 && m0 + ew * 32 < M && col0 < N) {
+          // fp32 output: the warp's 32x32 block goes through shared memory (128-byte rows, 16-byte chunks
+          // XOR-swizzled by row so that the 32 row-writes of one instruction spread over all banks) and leaves
+          // as one TMA store, or one TMA reduce-add when accumulating: C is never read into the SM, the stores
+          // are full lines, and the tensor map clips ragged edges.
+          float* cbuf = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 1024 +
+                                                 (ew * 2 + (c & 1)) * C_STAGE_BYTES);
+          bulk_wait_group_read<1>();               // the store that last used this buffer has read it
+          __syncwarp();
 #pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
-                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                if (accumulate) {
-                  const float4 p = reinterpret_cast<const float4*>(crow)[v];
-                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                }
-                reinterpret_cast<float4*>(crow)[v] = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j) {
-                const float x = __uint_as_float(r[j]);
-                crow[j] = accumulate ? crow[j] + x : x;
-              }
-            }
+          for (int v = 0; v < 8; ++v) {
+            const float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
+                                         __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+            reinterpret_cast<float4*>(cbuf + lane * 32)[v ^ (lane & 7)] = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (accumulate) tma_reduce_add_2d_bulk(&tmap_c, cbuf, col0, m0 + ew * 32);
+            else tma_store_2d_bulk(&tmap_c, cbuf, col0, m0 + ew * 32);
+            bulk_commit_group();
           }
         }
       }
@@ -265,6 +273,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->acc_empty[acc]);
     }
+    if (EPI == kEpiAccumF32 && lane == 0) bulk_wait_group<0>();   // staged blocks must leave before the CTA does
   }
 
   tc_fence_before();
@@ -352,26 +361,67 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// fp32 tensor map of C with 32x32 boxes and 128-byte swizzle (epilogue staging layout).
+static int make_tmap_c_f32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes) {
+  EncodeFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 static int launch(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, int num_sms,
                   cudaStream_t stream) {
   auto kern = gemm_kernel<A_MN, B_MN, EPI>;
+  constexpr int smem_bytes = EPI == kEpiAccumF32 ? SMEM_BYTES_F32 : SMEM_BYTES;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess)
       return -2;
     configured = true;
   }
+  CUtensorMap tc = ta;      // unused by the bf16 epilogue
+  if (EPI == kEpiAccumF32) {
+    const int rc = make_tmap_c_f32(&tc, g.c, g.N, g.M, static_cast<uint64_t>(g.ldc) * 4);
+    if (rc != 0) return rc;
+  }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, g.c, g.ldc, g.M, g.N, g.K, g.accumulate,
+  kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(ta, tb, tc, g.c, g.ldc, g.M, g.N, g.K, g.accumulate,
                                                   g.status, next_sched_slot());
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// 0: choose by shape, 128 / 256: forced by PIPER_GEMM_TILE
+static int forced_tile() {
+  static int v = -1;
+  if (v < 0) {
+    const char* env = getenv("PIPER_GEMM_TILE");
+    v = env == nullptr ? 0 : atoi(env);
+    if (v != 128 && v != 256) v = 0;
+  }
+  return v;
+}
+
 int gemm_bf16_launch(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
+  {
+    // 256x256 tiles move a third fewer operand bytes per flop.  Measured on B200: they win for bf16 outputs once
+    // there is at least one tile per SM; with the fp32 read-modify-write epilogue, whose exposed drain is twice
+    // as long, only for long contractions.
+    const int tile = g.tile != 0 ? g.tile : forced_tile();
+    const long long tiles256 = static_cast<long long>((g.M + 255) / 256) * ((g.N + 255) / 256);
+    const bool fits = g.M >= 256 && g.N >= 256 && tiles256 >= num_sms;
+    const bool pays = g.epilogue == kEpiStoreBf16 || g.K >= 8192;
+    if (tile == 256 || (tile == 0 && fits && pays))
+      return gemm256_bf16_launch(g, num_sms, next_sched_slot(), stream);
+  }
   CUtensorMap ta, tb;
   int rc;
   // K-major operand: dims {K, rows}, box {64, tile rows}.

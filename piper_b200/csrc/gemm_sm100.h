@@ -30,11 +30,17 @@ struct GemmArgs {
   int epilogue;     // kEpi*
   int accumulate;   // only for kEpiAccumF32
   int* status;      // device int, 0 = ok (see ptx.cuh)
+  int tile = 0;     // 0: chosen by shape (or PIPER_GEMM_TILE); 128 / 256: that CTA tile height
 };
 
 // Returns 0 on success, a negative code for a launch/set-up failure, or the
 // CUresult of a failed tensor-map encode.
 int gemm_bf16_launch(const GemmArgs& args, int num_sms, cudaStream_t stream);
+
+// Same contract with 256x256 tiles per CTA (gemm256_sm100.cu).  sched: two zeroed ints of device memory for the
+// dynamic tile scheduler (rearmed by the kernel), or null for static tile striding.  gemm_bf16_launch picks
+// between the two tile shapes; PIPER_GEMM_TILE=128 or 256 forces one.
+int gemm256_bf16_launch(const GemmArgs& args, int num_sms, int* sched, cudaStream_t stream);
 
 enum : int {
   kGroupedFwd = 0,     // Y[rows, N]  = X[rows, K] * W[e]^T

@@ -287,9 +287,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 reinterpret_cast<float4*>(crow)[v] = o;
               }
             } else {
-              for (int j = 0; j < 32 && col0 + j < out_cols; ++j) {
-                const float x = __uint_as_float(r[j]);
-                crow[j] = p.accumulate ? crow[j] + x : x;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {      // constant indices keep r[] in registers
+                if (col0 + j < out_cols) {
+                  const float x = __uint_as_float(r[j]);
+                  crow[j] = p.accumulate ? crow[j] + x : x;
+                }
               }
             }
           } else {
@@ -305,8 +308,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 reinterpret_cast<uint4*>(crow)[v] = o;
               }
             } else {
-              for (int j = 0; j < 32 && col0 + j < out_cols; ++j)
-                crow[j] = __float2bfloat16(__uint_as_float(r[j]));
+#pragma unroll
+              for (int j = 0; j < 32; ++j)        // constant indices keep r[] in registers
+                if (col0 + j < out_cols) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
             }
           }
         }

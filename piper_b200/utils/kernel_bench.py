@@ -41,6 +41,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-cublas", action="store_true", help="skip the library GEMM comparison")
+    ap.add_argument("--tile", type=int, default=0, choices=(0, 128, 256), help="force the GEMM CTA tile height")
     args = ap.parse_args(argv)
     global _time
     _base_time = _time
@@ -64,7 +65,7 @@ def main(argv=None):
         a = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
         b = torch.randn(N, K, device=dev, dtype=torch.bfloat16)
         c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
-        ms = _time(lambda: native.lib().gemm(a, b, c, False, False, False, st), flush=flush)
+        ms = _time(lambda: native.lib().gemm_tiled(a, b, c, False, False, False, st, args.tile), flush=flush)
         ms_ref = float("nan") if args.no_cublas else _time(lambda: torch.matmul(a, b.t(), out=c), flush=flush)
         fl = 2.0 * M * N * K
         rows.append({"kernel": f"gemm_fwd:{name}", "ms": ms, "tflops": fl / ms / 1e9, "cublas_ms": ms_ref,
@@ -72,10 +73,10 @@ def main(argv=None):
         # dgrad and wgrad layouts
         dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
         dx = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
-        ms = _time(lambda: native.lib().gemm(dy, b, dx, False, True, False, st), flush=flush)
+        ms = _time(lambda: native.lib().gemm_tiled(dy, b, dx, False, True, False, st, args.tile), flush=flush)
         rows.append({"kernel": f"gemm_dgrad:{name}", "ms": ms, "tflops": fl / ms / 1e9})
         dw = torch.zeros(N, K, device=dev, dtype=torch.float32)
-        ms = _time(lambda: native.lib().gemm(dy, a, dw, True, True, True, st), flush=flush)
+        ms = _time(lambda: native.lib().gemm_tiled(dy, a, dw, True, True, True, st, args.tile), flush=flush)
         rows.append({"kernel": f"gemm_wgrad_f32acc:{name}", "ms": ms, "tflops": fl / ms / 1e9})
         del a, b, c, dy, dx, dw
     attn_shapes = [(1, 4096, 32, 8, 128), (1, 4096, 32, 4, 128)]

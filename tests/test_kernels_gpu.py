@@ -58,6 +58,37 @@ def test_gemm_dgrad_and_wgrad_layouts(M, N, K):
     assert _rel_err(c2, as_.float().t() @ b.float().t()) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (200, 328, 136), (2304, 4608, 192)])
+def test_gemm_256_tile_all_layouts(M, N, K):
+    """The 256x256-tile kernel against fp32 references: every operand layout, both epilogues, ragged edges and
+    (last shape) more tiles than SMs so that CTAs walk several tiles and reuse their accumulator halves."""
+    from piper_b200.ops import native
+
+    torch.manual_seed(3)
+    st = native.status_tensor()
+    lib = native.lib()
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    at, bt = a.t().contiguous(), b.t().contiguous()          # [K, M], [K, N]
+    ref = a.float() @ b.float().t()
+    for a_op, a_mn in ((a, False), (at, True)):
+        for b_op, b_mn in ((b, False), (bt, True)):
+            c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            lib.gemm_tiled(a_op, b_op, c, a_mn, b_mn, False, st, 256)
+            assert _rel_err(c, ref) < 1e-2, (a_mn, b_mn)
+    acc = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    want = acc + ref
+    lib.gemm_tiled(at, bt, acc, True, True, True, st, 256)
+    assert _rel_err(acc, want) < 1e-2
+    c128 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    c256 = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    lib.gemm_tiled(a, b, c128, False, False, False, st, 128)
+    lib.gemm_tiled(a, b, c256, False, False, False, st, 256)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(c128, c256)      # same k order and fp32 accumulation: identical bits
+
+
 def test_linear_op_autograd():
     from piper_b200 import ops
 

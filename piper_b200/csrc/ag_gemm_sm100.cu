@@ -52,7 +52,7 @@ struct Barriers {
   uint64_t acc_empty[2];
   uint64_t g_full[GATHER_BUFS];
   uint32_t tmem_base;
-  int g_block[8];            // weight block of the gather chunk in flight (-1: local copy, not counted)
+  int g_block[16];           // weight block of the gather chunk in flight (-1: local copy, not counted)
 };
 
 // Geometry shared by the producer and the gather warp.
@@ -225,12 +225,21 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 3) {
     // ------------------------------------------------------ gather warp
     if (lane == 0 && gathered) {
-      const int per_pass = tiles_n * (BN / 64) * k_blocks;
-      const int total = 2 * per_pass;        // pass 0: boxes of other ranks, pass 1: this rank's own boxes
+      // Chunk c = (64-row box, k-block).  Boxes of other ranks come first, in the order the GEMM reaches them
+      // (the circular range that starts right after this rank's rows), then this rank's own boxes.
+      const int total_boxes = (N + 63) / 64;
+      int my_first = me * rows_per_shard / 64;
+      if (my_first > total_boxes) my_first = total_boxes;
+      int my_last = ((me + 1) * rows_per_shard < N ? (me + 1) * rows_per_shard : N);
+      my_last = (my_last + 63) / 64;
+      const int my_count = my_last > my_first ? my_last - my_first : 0;
+      const int remote_boxes = total_boxes - my_count;
+      const int total = total_boxes * k_blocks;
+      constexpr int PENDING = 3;             // stores that may still be in flight when the next one is issued
       uint32_t n = 0;                        // chunks whose load has been issued
+      uint32_t stored = 0, counted = 0;      // chunks whose store has been issued / whose arrival has been counted
       int src_x[GATHER_BUFS] = {0, 0, 0, 0}, src_row[GATHER_BUFS] = {0, 0, 0, 0};
       bool ok = true;
-      // chunk i: load at trip i, store at trip i + GATHER_AHEAD, counted at trip i + GATHER_AHEAD + 1
       auto store_chunk = [&](uint32_t i) -> bool {
         const int b = i % GATHER_BUFS;
         if (!mbar_wait(&bars->g_full[b], (i / GATHER_BUFS) & 1, status)) return false;
@@ -238,48 +247,46 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         return true;
       };
-      auto count_chunk = [&](uint32_t i) {
-        const int nb = bars->g_block[i & 7];
-        if (nb >= 0) {
-          asm volatile("fence.proxy.async;" ::: "memory");     // async-proxy stores -> generic-proxy counter
-          __threadfence();
-          atomicAdd(ready + nb, 1);
+      auto count_upto = [&](uint32_t end) {   // stores [counted, end) are complete: publish them
+        if (end <= counted) return;
+        asm volatile("fence.proxy.async;" ::: "memory");       // async-proxy stores -> generic-proxy counters
+        __threadfence();
+        for (; counted < end; ++counted) {
+          const int nb = bars->g_block[counted & 15];
+          if (nb >= 0) atomicAdd(ready + nb, 1);
         }
       };
-      while (ok) {
+      int c = atomicAdd(gather_next, 1);
+      while (ok && c < total) {
         if (*reinterpret_cast<volatile int*>(status) != 0) { ok = false; break; }
-        const int c = atomicAdd(gather_next, 1);
-        if (c >= total) break;
-        const int pass = c / per_pass;
-        const int rem = c - pass * per_pass;
-        const int q = rem / k_blocks;
-        const int kb = rem - q * k_blocks;
-        const int nb = geo.block_at(q / (BN / 64));
-        const int row = nb * BN + 64 * (q % (BN / 64));
-        if (row >= N) continue;
+        const int next_c = atomicAdd(gather_next, 1);   // claimed now, used next trip: its latency is hidden
+        const int bi = c / k_blocks;
+        const int kb = c - bi * k_blocks;
+        const bool remote = bi < remote_boxes;
+        const int box = remote ? (my_first + my_count + bi) % total_boxes : my_first + (bi - remote_boxes);
+        const int row = box * 64;
         const int p = geo.owner(row);
-        if ((pass == 0) != (p != me)) continue;
         const int b = n % GATHER_BUFS;
-        // the buffer's previous store (issued one trip ago) must have read it before it is overwritten
+        // the store that last used this buffer (issued one trip ago) must have read it before it is overwritten
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         src_x[b] = kb * BK;
         src_row[b] = row;
-        bars->g_block[n & 7] = p != me ? nb : -1;
+        bars->g_block[n & 15] = remote ? row / BN : -1;
         mbar_arrive_expect_tx(&bars->g_full[b], BOX_BYTES);
         tma_load_2d(gbuf + b * BOX_BYTES, &peers.m[p], &bars->g_full[b], kb * BK, row - p * rows_per_shard);
         ++n;
         if (n > GATHER_AHEAD) {
-          if (!store_chunk(n - 1 - GATHER_AHEAD)) { ok = false; break; }
-          if (n > GATHER_AHEAD + 1) {
-            asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // all but the newest store are complete
-            count_chunk(n - 2 - GATHER_AHEAD);
+          if (!store_chunk(stored)) { ok = false; break; }
+          ++stored;
+          if (stored > PENDING) {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(PENDING) : "memory");
+            count_upto(stored - PENDING);
           }
         }
+        c = next_c;
       }
-      // drain: chunks [first_unstored, n) still sit in shared memory (or are on their way into it)
-      const uint32_t first_unstored = n > GATHER_AHEAD ? n - GATHER_AHEAD : 0;
-      uint32_t stored = first_unstored;
-      for (uint32_t i = first_unstored; i < n; ++i) {
+      // drain: chunks [stored, n) still sit in shared memory (or are on their way into it)
+      for (uint32_t i = stored; i < n; ++i) {
         if (ok && store_chunk(i)) {
           stored = i + 1;
         } else {
@@ -288,9 +295,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-      const uint32_t first_uncounted = first_unstored > 0 ? first_unstored - 1 : 0;
-      if (ok)
-        for (uint32_t i = first_uncounted; i < stored; ++i) count_chunk(i);
+      if (ok) count_upto(stored);
     }
   } else if (warp >= 4) {
     const int ew = warp - 4;

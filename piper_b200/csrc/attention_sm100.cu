@@ -28,10 +28,27 @@
 // Every mbarrier wait is bounded (see ptx.cuh); on expiry a status code is
 // recorded and the CTA unwinds and frees its TMEM.
 #include "attention_sm100.h"
+
+#include <cstdlib>
+
 #include "ptx.cuh"
 
 namespace piper {
 namespace {
+
+// 0: waits suspend inside mbarrier.try_wait; 1: waits poll mbarrier.test_wait (set from PIPER_ATTN_SPIN).
+__constant__ int c_attn_spin;
+
+// Bounded wait on an mbarrier phase (see mbar_wait in ptx.cuh), in either of the two forms above.
+__device__ __forceinline__ bool await(uint64_t* bar, uint32_t parity, int* status) {
+  if (c_attn_spin == 0) return mbar_wait(bar, parity, status);
+  for (uint32_t i = 0; i < kMaxMbarPolls; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 4095u) == 4095u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+  }
+  if (status != nullptr) atomicCAS(status, 0, kStatusMbarTimeout);
+  return false;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -174,11 +191,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       if (!ok) {
         // Unwinding after a failed wait: let the copies already issued land
         // before the CTA and its shared memory go away.
-        mbar_wait(&bars->q_full, 0, nullptr);
+        await(&bars->q_full, 0, nullptr);
         for (int jj = kj - 1; jj >= 0 && jj >= kj - 2; --jj)
-          mbar_wait(&bars->k_full[jj & 1], (jj >> 1) & 1, nullptr);
+          await(&bars->k_full[jj & 1], (jj >> 1) & 1, nullptr);
         for (int jj = vj - 1; jj >= 0 && jj >= vj - 2; --jj)
-          mbar_wait(&bars->v_full[jj & 1], (jj >> 1) & 1, nullptr);
+          await(&bars->v_full[jj & 1], (jj >> 1) & 1, nullptr);
       }
     }
   } else if (warp == 5) {
@@ -188,7 +205,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, HD, false, true);
       const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
-      bool ok = mbar_wait(&bars->q_full, 0, status);
+      bool ok = await(&bars->q_full, 0, status);
       // Two queues served in whatever order their inputs arrive: S of block s_next (needs K and a free TMEM
       // stage) and P V of block p_next (needs the probabilities, V and a free output stage).
       int s_next = 0, p_next = 0;
@@ -262,7 +279,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int s = j & 1;
       const bool diag = (j == qblk);
-      if (!mbar_wait(&bars->s_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+      if (!await(&bars->s_full[s], (j >> 1) & 1, status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t ts = tmem_s + lane_sel + s * 128 + wg * 64;
       uint32_t sv[64];
@@ -284,12 +301,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       }
       xbuf[(s * 2 + wg) * 128 + row] = mx;
       mbar_arrive(&bars->mx_full[s]);
-      if (!mbar_wait(&bars->mx_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+      if (!await(&bars->mx_full[s], (j >> 1) & 1, status)) { ok = false; break; }
       mx = fmaxf(mx, xbuf[(s * 2 + (wg ^ 1)) * 128 + row]);
       const float m_new = fmaxf(m_run, mx);
       const float alpha = fast_exp2((m_run - m_new) * scale_log2);
       const float msc = m_new * scale_log2;
-      if (j > 0 && !mbar_wait(&bars->p_empty, (j - 1) & 1, status)) { ok = false; break; }
+      if (j > 0 && !await(&bars->p_empty, (j - 1) & 1, status)) { ok = false; break; }
       float rs = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -309,7 +326,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       mbar_arrive(&bars->p_full);
       if (j > 0) {
         const int sb = (j - 1) & 1;
-        if (!mbar_wait(&bars->o_full[sb], ((j - 1) >> 1) & 1, status)) { ok = false; break; }
+        if (!await(&bars->o_full[sb], ((j - 1) >> 1) & 1, status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t to = tmem_o + lane_sel + sb * HD + wg * HH;
 #pragma unroll
@@ -332,13 +349,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       // total row sum = this group's partial + the other group's
       xbuf[(4 + wg) * 128 + row] = l_run;
       mbar_arrive(&bars->l_full);
-      ok = mbar_wait(&bars->l_full, 0, status);
+      ok = await(&bars->l_full, 0, status);
     }
     if (ok) {
       const float l_tot = l_run + xbuf[(4 + (wg ^ 1)) * 128 + row];
       const int jj = n_blocks - 1;
       const int sb = jj & 1;
-      if (mbar_wait(&bars->o_full[sb], (jj >> 1) & 1, status)) {
+      if (await(&bars->o_full[sb], (jj >> 1) & 1, status)) {
         tc_fence_after();
         const uint32_t to = tmem_o + lane_sel + sb * HD + wg * HH;
         const float inv = 1.f / l_tot;
@@ -513,7 +530,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       int it = 0;
       for (; it < n_iter; ++it) {
         const int st = it % L::Y_STAGES;
-        if (!mbar_wait(&bars->y_empty[st], ((it / L::Y_STAGES) & 1) ^ 1, status)) break;
+        if (!await(&bars->y_empty[st], ((it / L::Y_STAGES) & 1) ^ 1, status)) break;
         const int hh = (MODE == 0) ? hy : g * group + it / tiles_per_head;   // query head
         const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;      // streamed tile index
         const int yrow = static_cast<int>(tok0) + ti * 64;
@@ -533,9 +550,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       }
       if (it < n_iter) {
         // Unwinding: wait (bounded) for the copies in flight.
-        mbar_wait(&bars->x_full, 0, nullptr);
+        await(&bars->x_full, 0, nullptr);
         for (int jj = it - 1; jj >= 0 && jj > it - 1 - L::Y_STAGES; --jj)
-          mbar_wait(&bars->y_full[jj % L::Y_STAGES], (jj / L::Y_STAGES) & 1, nullptr);
+          await(&bars->y_full[jj % L::Y_STAGES], (jj / L::Y_STAGES) & 1, nullptr);
       }
     }
   } else if (warp == 5) {
@@ -547,7 +564,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       const uint32_t x2 = smem_u32(smem + L::X2_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
       const uint32_t ds_addr = smem_u32(smem + L::DS_OFF);
-      bool ok = mbar_wait(&bars->x_full, 0, status);
+      bool ok = await(&bars->x_full, 0, status);
       // Two queues served in whatever order their inputs arrive: S'/dP' of tile s_next needs its streamed tile
       // and a free TMEM stage; the accumulation of tile a_next needs the P'/dS' tiles the threads wrote.  A fixed
       // order would let a streamed tile that is still in flight hold back the accumulation that frees the
@@ -663,9 +680,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         }
         // Bounded wait instead of a named barrier: a thread that gave up on
         // an earlier wait must not strand the others here.
-        if (!mbar_wait(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+        if (!await(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       }
-      if (!mbar_wait(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+      if (!await(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       tc_fence_after();
       // Causal mask is needed only where the streamed tile overlaps the
       // stationary rows: element (x row, y col) is kept iff key <= query.
@@ -702,14 +719,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           dw[i] = pack_bf16x2(d[0], d[1]);
         }
         // the tiles were last read by the MMAs of the previous iteration
-        if (it >= 1 && !mbar_wait(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
+        if (it >= 1 && !await(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
         if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
         store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
       }
       fence_proxy_async_smem();
       mbar_arrive(&bars->t_full);
     }
-    if (ok && mbar_wait(&bars->acc_full, 0, status)) {
+    if (ok && await(&bars->acc_full, 0, status)) {
       tc_fence_after();
       const long long tok = tok0 + xpos;
       // MODE 0 writes dQ of head hy; MODE 1 writes dK and dV of kv head g.
@@ -748,6 +765,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
   }
 }
 
+void configure_waits() {
+  static bool done = false;
+  if (done) return;
+  const char* env = getenv("PIPER_ATTN_SPIN");
+  const int spin = (env != nullptr && env[0] == '1') ? 1 : 0;
+  cudaMemcpyToSymbol(c_attn_spin, &spin, sizeof(int));
+  done = true;
+}
+
 template <typename K>
 int set_smem(K kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess
@@ -764,6 +790,7 @@ int attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int Hq, int H
              float softmax_scale, int* status, cudaStream_t st) {
   if (S % 128 != 0 || Hq % Hkv != 0 || (hd != 64 && hd != 128)) return -1;
   if (B == 0) return 0;
+  configure_waits();
   const long long T = static_cast<long long>(B) * S;
   const uint64_t W = static_cast<uint64_t>(Hq + 2 * Hkv) * hd;
   CUtensorMap tm;
@@ -822,6 +849,7 @@ int attn_bwd(const void* qkv, const void* out, const void* d_out, const float* l
              cudaStream_t st) {
   if (S % 128 != 0 || Hq % Hkv != 0 || (hd != 64 && hd != 128)) return -1;
   if (B == 0) return 0;
+  configure_waits();
   if (hd == 128)
     return attn_bwd_impl<128>(qkv, out, d_out, lse, delta, d_qkv, B, S, Hq, Hkv, softmax_scale, status, st);
   return attn_bwd_impl<64>(qkv, out, d_out, lse, delta, d_qkv, B, S, Hq, Hkv, softmax_scale, status, st);

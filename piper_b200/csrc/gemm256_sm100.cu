@@ -66,6 +66,9 @@ gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + BK - 1) / BK;
+  // Tiles that run at the same time should share operands: walk the dimension with fewer tiles fastest, so a
+  // wave of CTAs covers all of it and the operand of the long dimension streams through L2 once.
+  const bool n_fast = tiles_n < tiles_m;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -104,8 +107,8 @@ gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (mbar_wait(&bars->empty[s], ph ^ 1, status)) mbar_arrive(&bars->full[s]);   // end marker, no bytes
           break;
         }
-        const int m0 = (tile % tiles_m) * BM;
-        const int n0 = (tile / tiles_m) * BN;
+        const int m0 = (n_fast ? tile / tiles_n : tile % tiles_m) * BM;
+        const int n0 = (n_fast ? tile % tiles_n : tile / tiles_m) * BN;
         ++n_local;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
@@ -207,8 +210,8 @@ gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!mbar_wait(&bars->acc_full, local_tile & 1, status)) break;
       const int tile = *reinterpret_cast<volatile int*>(&bars->acc_tile[local_tile & 1]);
       if (tile < 0) break;
-      const int m0 = (tile % tiles_m) * BM;
-      const int n0 = (tile / tiles_m) * BN;
+      const int m0 = (n_fast ? tile / tiles_n : tile % tiles_m) * BM;
+      const int n0 = (n_fast ? tile % tiles_n : tile / tiles_m) * BN;
       tc_fence_after();
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {

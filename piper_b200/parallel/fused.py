@@ -154,7 +154,7 @@ class FusedExpertExchange:
         from ..ops.moe import row_capacity
         self.ranks, self.group = list(ranks), group
         self.ep = len(ranks)
-        self.me = self.ranks.index(dist.get_rank())
+        self.me = self.ranks.index(dist.get_rank()) if self.ep > 1 else 0
         self.T, self.D, self.E, self.k = tokens, dim, experts, k
         self.El = experts // self.ep
         self.cap = row_capacity(tokens, k, self.El)
@@ -172,7 +172,8 @@ class FusedExpertExchange:
         self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.epoch = 0
         torch.cuda.synchronize()
-        dist.barrier(group=group)
+        if self.ep > 1:
+            dist.barrier(group=group)
 
     def dispatch(self, x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor):
         lib = native.lib()

@@ -30,6 +30,8 @@ class SymmetricBuffer:
         nbytes = (int(nbytes) + 255) // 256 * 256
         local = lib.symm_alloc(nbytes)
         handle = lib.symm_export(local)
+        if len(ranks) == 1:
+            return cls(local, [local.data_ptr()], 0, [])       # single rank: nothing to exchange
         me = dist.get_rank()
         my_index = list(ranks).index(me)
         gathered: list = [None] * len(ranks)

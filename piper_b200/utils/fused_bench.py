@@ -2,6 +2,11 @@
 
 ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m piper_b200.utils.fused_bench``
 
+``python -m piper_b200.utils.fused_bench --local f1|f2|f3 [--iters n]`` runs one of the kernels in a single
+process on one GPU with every "peer" buffer in that GPU's own memory (F1: a group of one; F2: two weight shards
+that are both local; F3: an expert group of one), which is the form a profiler can capture: the kernels take the
+same code paths, only the loads and stores that would cross NVLink stay on the device.
+
 For each fused path the script times the kernel with CUDA events (warm-up, then the max over ranks of the
 median), and prints the achieved figure next to its roofline: the slower of FLOPs / measured bf16 GEMM peak and
 bytes that must cross NVLink / measured peer-copy bandwidth (770 GB/s per direction per GPU).  The NCCL
@@ -40,7 +45,99 @@ def _median_ms(fn, iters=8, warmup=3):
     return float(t.item())
 
 
+def local_main(which: str, iters: int) -> None:
+    """Single-process variants of the three kernels (see the module docstring)."""
+    from piper_b200.ops import moe as M, native
+    from piper_b200.parallel.fused import FusedExpertExchange
+    from piper_b200.parallel.symm import SymmetricBuffer
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = native.lib()
+    st = native.status_tensor()
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        return statistics.median(ts)
+
+    if which == "f1":
+        n = 128 * 1024 * 1024                      # 512 MiB of fp32 gradients: far larger than L2
+        buf = SymmetricBuffer.create(n * 2 + n * 4 + 2 * 8 + 512, [0], None)
+        g_off, f_off = n * 2, n * 2 + n * 4
+        buf.view(torch.float32, n, g_off).normal_()
+        master = torch.zeros(n, device=dev)
+        m, v = torch.zeros_like(master), torch.zeros_like(master)
+        counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        epoch = [0]
+
+        def f1():
+            epoch[0] += 1
+            lib.f1_rs_adam_ag(buf.offset_ptrs(g_off), buf.offset_ptrs(0), buf.offset_ptrs(f_off), master, m, v, 0, 1,
+                              epoch[0], 1e-4, 0.9, 0.95, 1e-8, 0.0, epoch[0], 1.0, counter, st, 5.0, 296)
+
+        ms = timed(f1)
+        hbm = n * (4 + 24 + 2 + 4)                 # grad read, master/m/v read+write, bf16 param write, grad clear
+        print(json.dumps({"path": "F1 local (group of one)", "elements": n, "ms": ms, "hbm_GBs": hbm / ms / 1e6,
+                          "fraction_of_hbm_peak": hbm / ms / 1e6 / 6549.4}))
+    elif which == "f2":
+        T, N, K, shards = 4096, 6144, 4096, 2
+        rows = N // shards
+        w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
+        x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+        parts = [w[p * rows:(p + 1) * rows].contiguous() for p in range(shards)]
+        full = torch.zeros(N, K, dtype=torch.bfloat16, device=dev)
+        scratch = torch.zeros((N + 255) // 256 + 2, dtype=torch.int32, device=dev)
+        y = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: lib.ag_gemm(x, [p.data_ptr() for p in parts], 0, full, scratch, y, N, rows, st))
+        fl = 2.0 * T * N * K
+        print(json.dumps({"path": "F2 local (two local shards, gathered mode)", "ms": ms, "tflops": fl / ms / 1e9,
+                          "fraction_of_gemm_peak": fl / ms / 1e9 / GEMM_TFLOPS,
+                          "max_abs_err_vs_full": float((full.float() - w.float()).abs().max())}))
+    else:
+        T, D, E, k = 4096, 2048, 128, 8
+        xt = torch.randn(T, D, device=dev).to(torch.bfloat16)
+        logits = torch.randn(T, E, device=dev).to(torch.bfloat16)
+        weights, idx, counts = M.moe_route(logits, k, True)
+        ex = FusedExpertExchange([0], None, T, D, E, k, timeout_s=5.0, num_ctas=296)
+        state = {}
+
+        def disp():
+            state["r"] = ex.dispatch(xt, idx, counts)
+
+        ms_d = timed(disp)
+        pos = state["r"][1]
+
+        def comb():
+            ex.epoch += 1
+            return ex.combine(pos, weights, T)
+
+        ms_c = timed(comb)
+        moved = T * k * D * 2
+        print(json.dumps({"path": "F3 local (group of one)", "dispatch_ms": ms_d, "combine_ms": ms_c,
+                          "dispatch_GBs": 2 * moved / ms_d / 1e6, "combine_GBs": moved / ms_c / 1e6}))
+    torch.cuda.synchronize()
+    native.check_status()
+
+
 def main():
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--local", choices=("f1", "f2", "f3"), default=None)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args()
+    if args.local:
+        return local_main(args.local, args.iters)
     from piper_b200.ops import moe as M, native
     from piper_b200.parallel.fused import FusedExpertExchange, ShardedWeight
     from piper_b200.parallel.symm import SymmetricBuffer

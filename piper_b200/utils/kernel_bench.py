@@ -80,6 +80,8 @@ def main(argv=None):
         rows.append({"kernel": f"gemm_wgrad_f32acc:{name}", "ms": ms, "tflops": fl / ms / 1e9})
         del a, b, c, dy, dx, dw
     attn_shapes = [(1, 4096, 32, 8, 128), (1, 4096, 32, 4, 128)]
+    if only_shape == "sweep":      # same token count and more, at other sequence lengths (per-CTA vs per-tile cost)
+        attn_shapes = [(4, 1024, 32, 8, 128), (2, 2048, 32, 8, 128), (1, 4096, 32, 8, 128), (1, 8192, 32, 8, 128)]
     if only_family and only_family != "attn":
         attn_shapes = []
     for (B, S, Hq, Hkv, hd) in attn_shapes:
@@ -88,14 +90,15 @@ def main(argv=None):
         g = torch.randn_like(out)
         ms = _time(lambda: ops.attention(qkv.detach(), B, S, Hq, Hkv, hd), flush=flush)
         fl = 4.0 * B * Hq * S * S * hd / 2
-        rows.append({"kernel": f"attn_fwd:Hq{Hq}kv{Hkv}", "ms": ms, "tflops": fl / ms / 1e9})
+        rows.append({"kernel": f"attn_fwd:B{B}S{S}Hq{Hq}kv{Hkv}", "ms": ms, "tflops": fl / ms / 1e9})
 
         def bwd():
             qkv.grad = None
             o = ops.attention(qkv, B, S, Hq, Hkv, hd)
             o.backward(g)
         ms_fb = _time(bwd, flush=flush)
-        rows.append({"kernel": f"attn_fwd+bwd:Hq{Hq}kv{Hkv}", "ms": ms_fb, "tflops": 3.5 * fl / ms_fb / 1e9})
+        rows.append({"kernel": f"attn_fwd+bwd:B{B}S{S}Hq{Hq}kv{Hkv}", "ms": ms_fb, "tflops": 3.5 * fl / ms_fb / 1e9,
+                     "bwd_ms": ms_fb - ms})
     if only_family and only_family != "elementwise":
         return _finish(rows, args, native)
     x = torch.randn(T, 4096, device=dev, dtype=torch.bfloat16)

@@ -50,6 +50,20 @@ __device__ __forceinline__ bool await(uint64_t* bar, uint32_t parity, int* statu
   return false;
 }
 
+// The same for a whole warp, with one outcome for all its lanes: a lane that gave up while its neighbours saw
+// the phase complete must not leave them alone at the next warp-wide synchronisation.
+__device__ __forceinline__ bool await_all(uint64_t* bar, uint32_t parity, int* status) {
+  return __all_sync(0xffffffffu, await(bar, parity, status));
+}
+
+// One arrival per warp: the lanes converge first, so whatever each of them wrote (and fenced) before the call
+// is ordered before the arrival that lane 0 performs for all of them.  256 threads arriving one by one on the
+// same barrier word would serialise in the shared-memory atomic unit several times per tile.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -126,14 +140,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       mbar_init(&bars->v_full[i], 1);
       mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], 256);
+      mbar_init(&bars->s_empty[i], 8);        // one arrival per softmax warp
       mbar_init(&bars->o_full[i], 1);
-      mbar_init(&bars->o_empty[i], 256);
-      mbar_init(&bars->mx_full[i], 256);
+      mbar_init(&bars->o_empty[i], 8);
+      mbar_init(&bars->mx_full[i], 8);
     }
-    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->p_full, 8);
     mbar_init(&bars->p_empty, 1);
-    mbar_init(&bars->l_full, 256);
+    mbar_init(&bars->l_full, 8);
     fence_mbar_init();
     tma_prefetch_desc(&tmap);
   }
@@ -279,7 +293,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
     for (int j = 0; j < n_blocks && ok; ++j) {
       const int s = j & 1;
       const bool diag = (j == qblk);
-      if (!await(&bars->s_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+      if (!await_all(&bars->s_full[s], (j >> 1) & 1, status)) { ok = false; break; }
       tc_fence_after();
       const uint32_t ts = tmem_s + lane_sel + s * 128 + wg * 64;
       uint32_t sv[64];
@@ -292,7 +306,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
         for (int i = 0; i < 32; ++i) { sv[i] = r0[i]; sv[32 + i] = r1[i]; }
       }
       tc_fence_before();
-      mbar_arrive(&bars->s_empty[s]);            // the scores live in registers from here on
+      warp_arrive(&bars->s_empty[s], lane);            // the scores live in registers from here on
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
@@ -300,13 +314,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
         mx = fmaxf(mx, v);
       }
       xbuf[(s * 2 + wg) * 128 + row] = mx;
-      mbar_arrive(&bars->mx_full[s]);
-      if (!await(&bars->mx_full[s], (j >> 1) & 1, status)) { ok = false; break; }
+      warp_arrive(&bars->mx_full[s], lane);
+      if (!await_all(&bars->mx_full[s], (j >> 1) & 1, status)) { ok = false; break; }
       mx = fmaxf(mx, xbuf[(s * 2 + (wg ^ 1)) * 128 + row]);
       const float m_new = fmaxf(m_run, mx);
       const float alpha = fast_exp2((m_run - m_new) * scale_log2);
       const float msc = m_new * scale_log2;
-      if (j > 0 && !await(&bars->p_empty, (j - 1) & 1, status)) { ok = false; break; }
+      if (j > 0 && !await_all(&bars->p_empty, (j - 1) & 1, status)) { ok = false; break; }
       float rs = 0.f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -323,10 +337,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
         store_row_chunk_sw128(smem + L::P_OFF + wg * 16384, row, c * 4, w);
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bars->p_full);
+      warp_arrive(&bars->p_full, lane);
       if (j > 0) {
         const int sb = (j - 1) & 1;
-        if (!await(&bars->o_full[sb], ((j - 1) >> 1) & 1, status)) { ok = false; break; }
+        if (!await_all(&bars->o_full[sb], ((j - 1) >> 1) & 1, status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t to = tmem_o + lane_sel + sb * HD + wg * HH;
 #pragma unroll
@@ -339,7 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
             o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha_prev + __uint_as_float(r[i]);
         }
         tc_fence_before();
-        mbar_arrive(&bars->o_empty[sb]);
+        warp_arrive(&bars->o_empty[sb], lane);
       }
       l_run = l_run * alpha + rs;
       m_run = m_new;
@@ -348,14 +362,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
     if (ok) {
       // total row sum = this group's partial + the other group's
       xbuf[(4 + wg) * 128 + row] = l_run;
-      mbar_arrive(&bars->l_full);
-      ok = await(&bars->l_full, 0, status);
+      warp_arrive(&bars->l_full, lane);
+      ok = await_all(&bars->l_full, 0, status);
     }
     if (ok) {
       const float l_tot = l_run + xbuf[(4 + (wg ^ 1)) * 128 + row];
       const int jj = n_blocks - 1;
       const int sb = jj & 1;
-      if (await(&bars->o_full[sb], (jj >> 1) & 1, status)) {
+      if (await_all(&bars->o_full[sb], (jj >> 1) & 1, status)) {
         tc_fence_after();
         const uint32_t to = tmem_o + lane_sel + sb * HD + wg * HH;
         const float inv = 1.f / l_tot;
@@ -486,10 +500,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->s_empty[i], 256);
-      mbar_init(&bars->v_full[i], 64);
+      mbar_init(&bars->s_empty[i], 8);        // one arrival per softmax warp
+      mbar_init(&bars->v_full[i], 2);        // warps 0 and 1 write the vectors
     }
-    mbar_init(&bars->t_full, 256);
+    mbar_init(&bars->t_full, 8);
     mbar_init(&bars->t_empty, 1);
     mbar_init(&bars->acc_full, 1);
     fence_mbar_init();
@@ -669,7 +683,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         if (wg == 0 && row < 64) {
           vec[vs * 128 + row] = pre_lse;
           vec[vs * 128 + 64 + row] = pre_delta;
-          mbar_arrive(&bars->v_full[st]);
+          warp_arrive(&bars->v_full[st], lane);
           if (it + 1 < n_iter) {
             const int hn = g * group + (it + 1) / tiles_per_head;
             const int tn = 2 * xb + (it + 1) % tiles_per_head;
@@ -680,9 +694,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         }
         // Bounded wait instead of a named barrier: a thread that gave up on
         // an earlier wait must not strand the others here.
-        if (!await(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+        if (!await_all(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       }
-      if (!await(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+      if (!await_all(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       tc_fence_after();
       // Causal mask is needed only where the streamed tile overlaps the
       // stationary rows: element (x row, y col) is kept iff key <= query.
@@ -696,7 +710,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         tmem_ld_32x32(ts + 64 + c * 32, dv);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&bars->s_empty[st]);   // S'/dP' of this stage now live in registers
+        warp_arrive(&bars->s_empty[st], lane);   // S'/dP' of this stage now live in registers
         uint32_t pw[16], dw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -719,14 +733,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           dw[i] = pack_bf16x2(d[0], d[1]);
         }
         // the tiles were last read by the MMAs of the previous iteration
-        if (it >= 1 && !await(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
+        if (it >= 1 && !await_all(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
         if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
         store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
       }
       fence_proxy_async_smem();
-      mbar_arrive(&bars->t_full);
+      warp_arrive(&bars->t_full, lane);
     }
-    if (ok && await(&bars->acc_full, 0, status)) {
+    if (ok && await_all(&bars->acc_full, 0, status)) {
       tc_fence_after();
       const long long tok = tok0 + xpos;
       // MODE 0 writes dQ of head hy; MODE 1 writes dK and dV of kv head g.

@@ -146,6 +146,8 @@ f1_kernel(const float* const* __restrict__ peer_grads, __nv_bfloat16* const* __r
             s.x += g[u][p].x; s.y += g[u][p].y; s.z += g[u][p].z; s.w += g[u][p].w;
           }
           adam_vec(s, w[u], mm[u], vv[u], h);
+          // this rank's own copy of the slice is read by nobody else: clear it for the next step right away
+          reinterpret_cast<float4*>(const_cast<float*>(gsrc[NP - 1]))[i] = make_float4(0.f, 0.f, 0.f, 0.f);
           reinterpret_cast<float4*>(master)[i] = w[u];
           reinterpret_cast<float4*>(m)[i] = mm[u];
           reinterpret_cast<float4*>(v)[i] = vv[u];
@@ -192,12 +194,15 @@ f1_kernel(const float* const* __restrict__ peer_grads, __nv_bfloat16* const* __r
   }
   __syncthreads();
   if (!ok_s) return;
-  // nobody reads the local gradients any more: clear them for the next step
+  // nobody reads the local gradients any more: clear the slices the peers have read (the fixed-size path has
+  // already cleared this rank's own slice)
   float4* lg = reinterpret_cast<float4*>(const_cast<float*>(peer_grads[my_rank]));
   const long long total_vec = shard_numel * dp / 4;
+  const long long own_lo = DP > 0 ? base / 4 : -1, own_hi = DP > 0 ? base / 4 + nvec : -1;
   const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
-  for (long long i = first; i < total_vec; i += stride) lg[i] = z;
+  for (long long i = first; i < total_vec; i += stride)
+    if (i < own_lo || i >= own_hi) lg[i] = z;
 }
 
 // ===================================================================== F3

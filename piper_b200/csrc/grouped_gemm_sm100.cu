@@ -377,8 +377,17 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GroupedParams& p,
 }  // namespace
 
 int grouped_gemm_launch(const GroupedGemmArgs& g, int num_sms, cudaStream_t st) {
-  if (g.num_groups <= 0 || g.num_groups > MAX_GROUPS || g.experts <= 0 || g.num_groups % g.experts != 0) return -1;
-  if (g.N % 8 != 0 || g.K % 8 != 0 || g.rows_capacity <= 0) return -1;
+  if (g.num_groups <= 0 || g.num_groups > MAX_GROUPS || g.experts <= 0 || g.num_groups % g.experts != 0) return -11;
+  if (g.N % 8 != 0 || g.K % 8 != 0 || g.rows_capacity < 0) return -12;
+  if (g.rows_capacity == 0) {
+    // A rank can receive no rows at all (every token routed to experts of other ranks): nothing to multiply.
+    // The weight gradient of such a step is zero.
+    if (g.mode == kGroupedWgrad && !g.accumulate) {
+      const size_t bytes = static_cast<size_t>(g.experts) * g.N * g.K * sizeof(float);
+      if (cudaMemsetAsync(g.out, 0, bytes, st) != cudaSuccess) return -3;
+    }
+    return 0;
+  }
   GroupedParams p;
   p.g_start = g.g_start;
   p.g_len = g.g_len;

@@ -23,6 +23,9 @@ import torch.distributed as dist
 
 NVLINK_GBS = 770.0
 GEMM_TFLOPS = 1397.3
+# A spin kernel of about half a millisecond goes in front of every timed region: the events then bracket device
+# time only, not the host's time to build tensor maps, allocate outputs and launch.
+HOST_LEAD_CYCLES = 1_000_000
 
 
 def _median_ms(fn, iters=8, warmup=3):
@@ -35,6 +38,7 @@ def _median_ms(fn, iters=8, warmup=3):
         dist.barrier()
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(HOST_LEAD_CYCLES)      # the host enqueues fn's kernels while this spins on the device
         s.record()
         fn()
         e.record()
@@ -63,6 +67,7 @@ def local_main(which: str, iters: int) -> None:
         ts = []
         for _ in range(iters):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(HOST_LEAD_CYCLES)  # the host enqueues fn's kernels while this spins on the device
             s.record()
             fn()
             e.record()
@@ -90,19 +95,25 @@ def local_main(which: str, iters: int) -> None:
         print(json.dumps({"path": "F1 local (group of one)", "elements": n, "ms": ms, "hbm_GBs": hbm / ms / 1e6,
                           "fraction_of_hbm_peak": hbm / ms / 1e6 / 6549.4}))
     elif which == "f2":
-        T, N, K, shards = 4096, 6144, 4096, 2
-        rows = N // shards
+        T, N, K = 4096, 6144, 4096
         w = (torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)
         x = torch.randn(T, K, device=dev).to(torch.bfloat16)
-        parts = [w[p * rows:(p + 1) * rows].contiguous() for p in range(shards)]
-        full = torch.zeros(N, K, dtype=torch.bfloat16, device=dev)
-        scratch = torch.zeros((N + 255) // 256 + 2, dtype=torch.int32, device=dev)
         y = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
-        ms = timed(lambda: lib.ag_gemm(x, [p.data_ptr() for p in parts], 0, full, scratch, y, N, rows, st))
         fl = 2.0 * T * N * K
-        print(json.dumps({"path": "F2 local (two local shards, gathered mode)", "ms": ms, "tflops": fl / ms / 1e9,
-                          "fraction_of_gemm_peak": fl / ms / 1e9 / GEMM_TFLOPS,
-                          "max_abs_err_vs_full": float((full.float() - w.float()).abs().max())}))
+        ms = timed(lambda: lib.gemm(x, w, y, False, False, False, st))
+        print(json.dumps({"path": "plain GEMM of the same shape", "ms": ms, "tflops": fl / ms / 1e9}))
+        for shards, gathered in ((2, False), (1, True), (2, True)):
+            rows = N // shards
+            parts = [w[p * rows:(p + 1) * rows].contiguous() for p in range(shards)]
+            full = torch.zeros(N, K, dtype=torch.bfloat16, device=dev) if gathered else None
+            scratch = torch.zeros((N + 255) // 256 + 2, dtype=torch.int32, device=dev) if gathered else None
+            ptrs = [p.data_ptr() for p in parts]
+            ms = timed(lambda: lib.ag_gemm(x, ptrs, 0, full, scratch, y, N, rows, st))
+            rec = {"path": f"F2 local: {shards} local shard(s), {'gathered' if gathered else 'direct'} mode", "ms": ms,
+                   "tflops": fl / ms / 1e9, "fraction_of_gemm_peak": fl / ms / 1e9 / GEMM_TFLOPS}
+            if gathered:
+                rec["max_abs_err_vs_full"] = float((full.float() - w.float()).abs().max())
+            print(json.dumps(rec))
     else:
         T, D, E, k = 4096, 2048, 128, 8
         xt = torch.randn(T, D, device=dev).to(torch.bfloat16)
@@ -170,12 +181,13 @@ def main():
     for ctas in (148, 296, 592, 1184):
         grads.normal_()
         ms = _median_ms(lambda: f1(ctas))
-        inbound = (world - 1) * shard * 4            # peers' gradient slices read by this rank
-        outbound = (world - 1) * shard * 2           # updated bf16 parameters stored to peers
-        roof_ms = max(inbound, outbound) / (NVLINK_GBS * 1e6)
+        # bytes crossing NVLink per direction and rank: this rank reads its slice of every peer's fp32 gradients
+        # (4 B/element) and every peer stores its updated bf16 slice into this rank's parameter buffer (2 B/element)
+        nvlink = (world - 1) * shard * (4 + 2)
+        roof_ms = nvlink / (NVLINK_GBS * 1e6)
         hbm_ms = (shard * (4 + 24 + 2) + n * 4) / (6549.4 * 1e6)
         rows.append({"path": "F1 rs+adam+ag", "ctas": ctas, "world": world, "elements": n, "ms": ms,
-                     "nvlink_in_GBs": inbound / ms / 1e6, "roofline_ms": max(roof_ms, hbm_ms),
+                     "nvlink_GBs_per_direction": nvlink / ms / 1e6, "roofline_ms": max(roof_ms, hbm_ms),
                      "fraction_of_roofline": max(roof_ms, hbm_ms) / ms})
     native.check_status()
     flat = torch.randn(n, device=dev)

@@ -97,3 +97,29 @@ def test_qwen3_moe_model_trains_on_one_gpu():
     native.check_status()
     assert all(v == v for v in first + last)
     assert sum(last) < sum(first) - 0.5, (first, last)
+
+
+def test_grouped_gemm_with_no_rows():
+    """A rank that receives no rows in an expert exchange: forward/input-gradient products are empty and the
+    weight gradient is zero (or left untouched when accumulating)."""
+    from piper_b200.ops import native
+
+    dev = torch.device("cuda")
+    E, N, K = 4, 256, 128
+    lib, st = native.lib(), native.status_tensor(dev)
+    w = torch.randn(E, N, K, device=dev, dtype=torch.bfloat16)
+    rows = torch.empty(0, K, device=dev, dtype=torch.bfloat16)
+    dy = torch.empty(0, N, device=dev, dtype=torch.bfloat16)
+    g_start = torch.zeros(2 * E, dtype=torch.int32, device=dev)
+    g_len = torch.zeros(2 * E, dtype=torch.int32, device=dev)
+    out = torch.empty(0, N, device=dev, dtype=torch.bfloat16)
+    lib.grouped_gemm(0, rows, None, w, out, g_start, g_len, E, N, K, False, st)
+    dx = torch.empty(0, K, device=dev, dtype=torch.bfloat16)
+    lib.grouped_gemm(1, None, dy, w, dx, g_start, g_len, E, N, K, False, st)
+    dw = torch.full((E, N, K), 3.0, device=dev)
+    lib.grouped_gemm(2, rows, dy, None, dw, g_start, g_len, E, N, K, True, st)
+    assert torch.all(dw == 3.0)
+    lib.grouped_gemm(2, rows, dy, None, dw, g_start, g_len, E, N, K, False, st)
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.all(dw == 0.0)

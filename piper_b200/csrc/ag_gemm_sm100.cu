@@ -8,11 +8,13 @@
 // warps) plus a gather warp per CTA.
 //
 // Gathered mode (a local full-size buffer is given): the gather warps of all
-// CTAs together pull every remote 64-row x 64-column weight box exactly once
-// over NVLink - a TMA load from the owner's shard into shared memory and a
-// TMA store into the local full buffer, several boxes in flight per CTA - and
-// count finished boxes per 256-row weight block in global memory.  Boxes are
-// handed out through one atomic counter in the order the GEMM needs them.
+// CTAs together copy every remote weight byte exactly once over NVLink - the
+// shards and the gathered weight are contiguous, so this is a flat copy in
+// pieces of up to 8 KiB: a bulk load from the owner's shard into shared
+// memory and a bulk store into the local full buffer, several pieces in
+// flight per CTA - and count finished pieces per 256-row weight block in
+// global memory.  Pieces are handed out through one atomic counter in the
+// order the GEMM needs them.
 // The GEMM walks weight blocks starting with the ones this rank owns (read
 // straight from its shard), so the tensor cores are busy while the first
 // remote blocks arrive; before it loads a block with remote rows the
@@ -55,36 +57,33 @@ struct Barriers {
   int g_block[16];           // weight block of the gather chunk in flight (-1: local copy, not counted)
 };
 
-// Geometry shared by the producer and the gather warp.
+// Geometry shared by the producer and the gather warp.  The gathered weight and every shard are contiguous
+// row-major memory, so the gather is a flat copy in pieces of `piece` bytes (a power of two that divides both a
+// shard and a 256-row weight block, so no piece straddles either).
 struct Geo {
   int N, rows_per_shard, num_peers, me, tiles_n, k_blocks, first_block;
-  __device__ int owner(int row) const {
-    const int p = row / rows_per_shard;
-    return p < num_peers ? p : num_peers - 1;
-  }
+  long long total_bytes, shard_bytes, block_bytes, my_lo, my_hi;   // byte ranges inside the gathered weight
+  int piece;
   // position in the walk over weight blocks (own blocks first) -> block index
   __device__ int block_at(int pos) const { return (first_block + pos) % tiles_n; }
-  // number of gather chunks the producer has to wait for before it may read this block from the full buffer
+  __device__ long long pieces_in(long long lo, long long hi) const { return hi > lo ? (hi - lo + piece - 1) / piece : 0; }
+  // number of gathered pieces the producer has to wait for before it may read this block from the full buffer
   __device__ int needed(int nb) const {
-    int boxes = 0;
-    for (int j = 0; j < BN / 64; ++j) {
-      const int row = nb * BN + 64 * j;
-      if (row < N && owner(row) != me) ++boxes;
-    }
-    return boxes * k_blocks;
+    const long long lo = nb * block_bytes;
+    const long long hi = lo + block_bytes < total_bytes ? lo + block_bytes : total_bytes;
+    const long long before_hi = hi < my_lo ? hi : my_lo;      // part of the block below this rank's rows
+    const long long after_lo = lo > my_hi ? lo : my_hi;       // part of the block above this rank's rows
+    return static_cast<int>(pieces_in(lo, before_hi) + pieces_in(after_lo, hi));
   }
+};
+
+struct ShardPtrs {
+  const uint8_t* p[kMaxPeers];
 };
 
 struct PeerMaps {
   CUtensorMap m[kMaxPeers];
 };
-
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(m)),
-               "r"(smem_u32(smem_src)), "r"(x), "r"(y)
-               : "memory");
-}
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -95,7 +94,8 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ PeerMaps peers,
                const __grid_constant__ CUtensorMap tmap_full, __nv_bfloat16* __restrict__ c, long long ldc, int M,
-               int N, int K, int rows_per_shard, int num_peers, int me, int gathered, int* scratch, int* status) {
+               int N, int K, int rows_per_shard, int num_peers, int me, int gathered, int* scratch, int* status,
+               const __grid_constant__ ShardPtrs shards, uint8_t* __restrict__ w_full, int piece) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -111,6 +111,12 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   geo.N = N; geo.rows_per_shard = rows_per_shard; geo.num_peers = num_peers; geo.me = me;
   geo.tiles_n = tiles_n; geo.k_blocks = k_blocks;
   geo.first_block = gathered ? (me * rows_per_shard) / BN % tiles_n : 0;
+  geo.total_bytes = static_cast<long long>(N) * K * 2;
+  geo.shard_bytes = static_cast<long long>(rows_per_shard) * K * 2;
+  geo.block_bytes = static_cast<long long>(BN) * K * 2;
+  geo.my_lo = geo.shard_bytes * me < geo.total_bytes ? geo.shard_bytes * me : geo.total_bytes;
+  geo.my_hi = geo.shard_bytes * (me + 1) < geo.total_bytes ? geo.shard_bytes * (me + 1) : geo.total_bytes;
+  geo.piece = piece;
   int* gather_next = scratch;            // [0]: next gather chunk
   int* ready = scratch + 2;              // [2 + block]: gathered chunks of that weight block
 
@@ -160,6 +166,23 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy flag read -> async-proxy tile loads
           }
         }
+        // where each of the tile's four 64-row weight boxes comes from (worked out once per tile: the k loop
+        // below has to issue a stage every few hundred cycles)
+        const CUtensorMap* bmap[BN / 64];
+        int brow[BN / 64];
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j) {
+          const int row = n0 + 64 * j;
+          int p = row / rows_per_shard;
+          int local = row - p * rows_per_shard;
+          if (p >= num_peers) {          // past the last weight row: an out-of-range box reads zeros
+            p = num_peers - 1;
+            local = rows_per_shard + (row - num_peers * rows_per_shard);
+          }
+          const bool from_full = gathered && (p != me || row >= N);
+          bmap[j] = from_full ? &tmap_full : &peers.m[p];
+          brow[j] = from_full ? row : local;
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -169,19 +192,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           mbar_arrive_expect_tx(&bars->full[s], STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &bars->full[s], kb * BK, m0);
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j) {
-            const int row = n0 + 64 * j;
-            int p = row / rows_per_shard;
-            int local = row - p * rows_per_shard;
-            if (p >= num_peers) {          // past the last weight row: an out-of-range box reads zeros
-              p = num_peers - 1;
-              local = rows_per_shard + (row - num_peers * rows_per_shard);
-            }
-            if (gathered && (p != me || row >= N))
-              tma_load_2d(sb + j * BOX_BYTES, &tmap_full, &bars->full[s], kb * BK, row);
-            else
-              tma_load_2d(sb + j * BOX_BYTES, &peers.m[p], &bars->full[s], kb * BK, local);
-          }
+          for (int j = 0; j < BN / 64; ++j)
+            tma_load_2d(sb + j * BOX_BYTES, bmap[j], &bars->full[s], kb * BK, brow[j]);
         }
       }
       if (!ok) {
@@ -225,25 +237,30 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else if (warp == 3) {
     // ------------------------------------------------------ gather warp
     if (lane == 0 && gathered) {
-      // Chunk c = (64-row box, k-block).  Boxes of other ranks come first, in the order the GEMM reaches them
-      // (the circular range that starts right after this rank's rows), then this rank's own boxes.
-      const int total_boxes = (N + 63) / 64;
-      int my_first = me * rows_per_shard / 64;
-      if (my_first > total_boxes) my_first = total_boxes;
-      int my_last = ((me + 1) * rows_per_shard < N ? (me + 1) * rows_per_shard : N);
-      my_last = (my_last + 63) / 64;
-      const int my_count = my_last > my_first ? my_last - my_first : 0;
-      const int remote_boxes = total_boxes - my_count;
-      const int total = total_boxes * k_blocks;
+      // Piece c of the flat copy: first the bytes above this rank's rows, then the bytes below them (the order in
+      // which the GEMM reaches the blocks), last this rank's own rows.  Large contiguous bulk copies keep the
+      // NVLink requests long.
+      // remote bytes in the circular order that starts at the GEMM's first block: [start, my_lo) (non-empty
+      // only when that block straddles the start of this rank's rows), [my_hi, end), [0, start); then own rows
+      const long long start = geo.first_block * geo.block_bytes < geo.my_lo ? geo.first_block * geo.block_bytes : geo.my_lo;
+      const long long seg_lo[4] = {start, geo.my_hi, 0, geo.my_lo};
+      const long long seg_hi[4] = {geo.my_lo, geo.total_bytes, start, geo.my_hi};
+      long long seg_first[5];
+      seg_first[0] = 0;
+      for (int i = 0; i < 4; ++i) seg_first[i + 1] = seg_first[i] + geo.pieces_in(seg_lo[i], seg_hi[i]);
+      const long long total = seg_first[4];
       constexpr int PENDING = 3;             // stores that may still be in flight when the next one is issued
-      uint32_t n = 0;                        // chunks whose load has been issued
-      uint32_t stored = 0, counted = 0;      // chunks whose store has been issued / whose arrival has been counted
-      int src_x[GATHER_BUFS] = {0, 0, 0, 0}, src_row[GATHER_BUFS] = {0, 0, 0, 0};
+      uint32_t n = 0;                        // pieces whose load has been issued
+      uint32_t stored = 0, counted = 0;      // pieces whose store has been issued / whose arrival has been counted
+      long long dst_off[GATHER_BUFS] = {0, 0, 0, 0};
+      uint32_t len[GATHER_BUFS] = {0, 0, 0, 0};
       bool ok = true;
-      auto store_chunk = [&](uint32_t i) -> bool {
+      auto store_piece = [&](uint32_t i) -> bool {
         const int b = i % GATHER_BUFS;
         if (!mbar_wait(&bars->g_full[b], (i / GATHER_BUFS) & 1, status)) return false;
-        tma_store_2d(&tmap_full, gbuf + b * BOX_BYTES, src_x[b], src_row[b]);
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(w_full + dst_off[b]),
+                     "r"(smem_u32(gbuf + b * BOX_BYTES)), "r"(len[b])
+                     : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         return true;
       };
@@ -256,27 +273,31 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (nb >= 0) atomicAdd(ready + nb, 1);
         }
       };
-      int c = atomicAdd(gather_next, 1);
+      long long c = atomicAdd(gather_next, 1);
       while (ok && c < total) {
         if (*reinterpret_cast<volatile int*>(status) != 0) { ok = false; break; }
-        const int next_c = atomicAdd(gather_next, 1);   // claimed now, used next trip: its latency is hidden
-        const int bi = c / k_blocks;
-        const int kb = c - bi * k_blocks;
-        const bool remote = bi < remote_boxes;
-        const int box = remote ? (my_first + my_count + bi) % total_boxes : my_first + (bi - remote_boxes);
-        const int row = box * 64;
-        const int p = geo.owner(row);
+        const long long next_c = atomicAdd(gather_next, 1);   // claimed now, used next trip: its latency is hidden
+        int seg = 0;
+        while (seg < 3 && c >= seg_first[seg + 1]) ++seg;
+        const long long off = seg_lo[seg] + (c - seg_first[seg]) * piece;
+        const long long end = seg_hi[seg];
+        const bool remote = seg < 3;
+        const uint32_t bytes = static_cast<uint32_t>(end - off < piece ? end - off : piece);
+        const int p = static_cast<int>(off / geo.shard_bytes);
         const int b = n % GATHER_BUFS;
         // the store that last used this buffer (issued one trip ago) must have read it before it is overwritten
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        src_x[b] = kb * BK;
-        src_row[b] = row;
-        bars->g_block[n & 15] = remote ? row / BN : -1;
-        mbar_arrive_expect_tx(&bars->g_full[b], BOX_BYTES);
-        tma_load_2d(gbuf + b * BOX_BYTES, &peers.m[p], &bars->g_full[b], kb * BK, row - p * rows_per_shard);
+        dst_off[b] = off;
+        len[b] = bytes;
+        bars->g_block[n & 15] = remote ? static_cast<int>(off / geo.block_bytes) : -1;
+        mbar_arrive_expect_tx(&bars->g_full[b], bytes);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_u32(gbuf + b * BOX_BYTES)), "l"(shards.p[p] + (off - p * geo.shard_bytes)), "r"(bytes),
+                     "r"(smem_u32(&bars->g_full[b]))
+                     : "memory");
         ++n;
         if (n > GATHER_AHEAD) {
-          if (!store_chunk(stored)) { ok = false; break; }
+          if (!store_piece(stored)) { ok = false; break; }
           ++stored;
           if (stored > PENDING) {
             asm volatile("cp.async.bulk.wait_group %0;" ::"n"(PENDING) : "memory");
@@ -285,9 +306,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         c = next_c;
       }
-      // drain: chunks [stored, n) still sit in shared memory (or are on their way into it)
+      // drain: pieces [stored, n) still sit in shared memory (or are on their way into it)
       for (uint32_t i = stored; i < n; ++i) {
-        if (ok && store_chunk(i)) {
+        if (ok && store_piece(i)) {
           stored = i + 1;
         } else {
           ok = false;
@@ -381,11 +402,20 @@ int ag_gemm_launch(const AgGemmArgs& g, int num_sms, cudaStream_t st) {
     configured = true;
   }
   if (gathered && cudaMemsetAsync(g.scratch, 0, sizeof(int) * (tiles_n + 2), st) != cudaSuccess) return -3;
+  // gather piece: the largest power of two up to 8 KiB that divides a shard and a 256-row block
+  const long long shard_bytes = static_cast<long long>(g.rows_per_shard) * g.K * 2;
+  const long long block_bytes = static_cast<long long>(BN) * g.K * 2;
+  int piece = BOX_BYTES;
+  while (piece > 16 && (shard_bytes % piece != 0 || block_bytes % piece != 0)) piece >>= 1;
+  ShardPtrs sp;
+  for (int p = 0; p < kMaxPeers; ++p)
+    sp.p[p] = static_cast<const uint8_t*>(g.w_shards[p < g.num_peers ? p : 0]);
   const int tiles = ((g.M + BM - 1) / BM) * tiles_n;
   const int grid = tiles < num_sms ? tiles : num_sms;
   ag_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, pm, tfull, static_cast<__nv_bfloat16*>(g.y), g.N, g.M,
                                                         g.N, g.K, g.rows_per_shard, g.num_peers, g.my_index,
-                                                        gathered ? 1 : 0, g.scratch, g.status);
+                                                        gathered ? 1 : 0, g.scratch, g.status, sp,
+                                                        static_cast<uint8_t*>(g.w_full), piece);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -17,6 +17,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "ptx.cuh"
 
 namespace piper {
@@ -296,6 +298,81 @@ __global__ void ep_dispatch_push_kernel(const __nv_bfloat16* __restrict__ x, con
   }
 }
 
+// The same dispatch with the rows leaving through the bulk-copy engine: a warp stages a token's row in shared
+// memory once and issues one bulk store (shared -> global, to local or peer memory) per destination row, two
+// tokens in flight per warp.  Large stores keep the NVLink packets full and leave the SM's load/store units
+// free.  Dynamic shared memory: warps_per_CTA * 2 * D * 2 bytes.
+__global__ void ep_dispatch_push_bulk_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
+                                             const int* __restrict__ counts, const int* __restrict__ seg_off,
+                                             int* __restrict__ cursor, int* __restrict__ pos,
+                                             __nv_bfloat16* const* __restrict__ peer_recv,
+                                             uint64_t* const* __restrict__ peer_flags, unsigned int* cta_counter,
+                                             int my_rank, int ep, int experts_local, long long T, int D, int k,
+                                             int cap, unsigned long long epoch) {
+  extern __shared__ __align__(128) uint8_t stage[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long w0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int vecs = D / 8;
+  const uint32_t row_bytes = static_cast<uint32_t>(D) * 2;
+  uint8_t* wbuf = stage + static_cast<size_t>(warp) * 2 * row_bytes;
+  int n = 0;
+  for (long long t = w0; t < T; t += warps, ++n) {
+    int d_l = 0, row_l = 0;
+    if (lane < k) {
+      const int e = idx[t * k + lane];
+      d_l = e / experts_local;
+      row_l = my_rank * cap + seg_off[e] + atomicAdd(cursor + e, 1);
+      pos[t * k + lane] = d_l * (ep * cap) + row_l;
+    }
+    uint8_t* buf = wbuf + (n & 1) * row_bytes;
+    if (lane == 0) bulk_wait_group_read<1>();      // the stores of two tokens ago have read this buffer
+    __syncwarp();
+    const uint4* src = reinterpret_cast<const uint4*>(x + t * D);
+    for (int i = lane; i < vecs; i += 32) reinterpret_cast<uint4*>(buf)[i] = src[i];
+    fence_proxy_async_smem();
+    __syncwarp();
+    for (int j = 0; j < k; ++j) {
+      const int d = __shfl_sync(0xffffffffu, d_l, j);
+      const int row = __shfl_sync(0xffffffffu, row_l, j);
+      if (lane == 0) {
+        __nv_bfloat16* dst = peer_recv[d] + static_cast<long long>(row) * D;
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                     "r"(smem_u32(buf)), "r"(row_bytes)
+                     : "memory");
+      }
+    }
+    if (lane == 0) bulk_commit_group();
+  }
+  if (lane == 0) {
+    bulk_wait_group<0>();                          // every row has been written
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
+  __syncwarp();
+  // zero the padding rows of every segment this rank owns in the peers' regions
+  const int E = ep * experts_local;
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (int e = blockIdx.x; e < E; e += gridDim.x) {
+    const int d = e / experts_local;
+    const int first = my_rank * cap + seg_off[e] + counts[e];
+    const int last = my_rank * cap + seg_off[e] + (counts[e] + 127) / 128 * 128;
+    uint4* base = reinterpret_cast<uint4*>(peer_recv[d] + static_cast<long long>(first) * D);
+    const long long nvec = static_cast<long long>(last - first) * (D / 8);
+    for (long long i = threadIdx.x; i < nvec; i += blockDim.x) base[i] = z;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *cta_counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < ep; ++p) st_release_sys(peer_flags[p] + my_rank, epoch);
+    }
+  }
+}
+
 // Waits for every source's "region complete" flag, then builds the group
 // table of the regions: group (src, l) starts at src*cap + padded prefix.
 __global__ void ep_wait_table_kernel(const uint64_t* __restrict__ flags, const int* __restrict__ meta,
@@ -395,6 +472,115 @@ __global__ void ep_combine_pull_kernel(const __nv_bfloat16* const* __restrict__ 
   }
 }
 
+// The same combine with the expert outputs arriving through the bulk-copy engine: per token a warp walks the row
+// in pieces of CHUNK bytes; for each piece lane 0 requests the k source pieces (from local or peer memory) into
+// shared memory with k bulk loads on one mbarrier, one piece ahead of the arithmetic, and the lanes then add the
+// k pieces with their router weights.  Dynamic shared memory: warps_per_CTA * 2 * k * CHUNK bytes + barriers.
+constexpr int kPullChunk = 1024;      // bytes of one row piece: 16 bf16 per lane
+
+__global__ void ep_combine_pull_bulk_kernel(const __nv_bfloat16* const* __restrict__ peer_out,
+                                            const int* __restrict__ pos, const float* __restrict__ weights,
+                                            __nv_bfloat16* __restrict__ out, const uint64_t* __restrict__ out_flags,
+                                            long long T, int D, int k, int ep, int cap, unsigned long long epoch,
+                                            unsigned long long timeout_ns, int* status) {
+  extern __shared__ __align__(128) uint8_t stage[];
+  __shared__ int ok_s;
+  __shared__ __align__(8) uint64_t bars[16];       // two per warp (up to 8 warps)
+  if (threadIdx.x == 0) ok_s = wait_flags(out_flags, ep, epoch, timeout_ns, status) ? 1 : 0;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    mbar_init(&bars[2 * warp], 1);
+    mbar_init(&bars[2 * warp + 1], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long region = static_cast<long long>(ep) * cap;
+  const int pieces = (D * 2 + kPullChunk - 1) / kPullChunk;        // per row
+  uint8_t* wbuf = stage + static_cast<size_t>(warp) * 2 * k * kPullChunk;
+  const long long w0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  // flat sequence of (token, piece) items of this warp; item i uses buffer and barrier i & 1
+  long long n_items = 0;
+  for (long long t = w0; t < T; t += warps) n_items += pieces;
+  const __nv_bfloat16* src_l = nullptr;      // lanes 0..k-1: source row of the token being requested
+  long long req_tok = -1;
+  auto request = [&](long long item) {       // all lanes call; lane j < k issues the load of source j
+    const long long t = w0 + (item / pieces) * warps;
+    const int piece = static_cast<int>(item % pieces);
+    if (t != req_tok) {
+      req_tok = t;
+      if (lane < k) {
+        const int p = pos[t * k + lane];
+        src_l = peer_out[static_cast<int>(p / region)] + (p % region) * D;
+      }
+    }
+    const int bytes = (piece + 1) * kPullChunk <= D * 2 ? kPullChunk : D * 2 - piece * kPullChunk;
+    uint64_t* bar = &bars[2 * warp + (item & 1)];
+    uint8_t* buf = wbuf + (item & 1) * k * kPullChunk;
+    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(bytes) * k);
+    __syncwarp();
+    if (lane < k) {
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(src_l) + piece * kPullChunk;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(buf + lane * kPullChunk)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                   : "memory");
+    }
+  };
+  __shared__ float wts[8][32];               // router weights of the token being summed, per warp
+  long long requested = 0, done = 0;
+  if (n_items > 0) { request(0); requested = 1; }
+  bool ok = true;
+  long long sum_tok = -1;
+  for (long long item = 0; item < n_items; ++item) {
+    const long long t = w0 + (item / pieces) * warps;
+    const int piece = static_cast<int>(item % pieces);
+    if (item + 1 < n_items) { request(item + 1); requested = item + 2; }   // one piece ahead
+    if (t != sum_tok) {
+      sum_tok = t;
+      __syncwarp();
+      if (lane < k) wts[warp][lane] = weights[t * k + lane];
+      __syncwarp();
+    }
+    ok = __all_sync(0xffffffffu, mbar_wait(&bars[2 * warp + (item & 1)], (item >> 1) & 1, status));
+    if (!ok) break;
+    done = item + 1;
+    const uint8_t* buf = wbuf + (item & 1) * k * kPullChunk;
+    const int col = piece * (kPullChunk / 2) + lane * 16;          // first of this lane's 16 columns
+    if (col < D) {
+      float acc[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        const float w = wts[warp][j];
+        const uint4* q = reinterpret_cast<const uint4*>(buf + j * kPullChunk + lane * 32);
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const uint4 v = q[h2];
+          const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float2 f = __bfloat1622float2(hh[c]);
+            acc[h2 * 8 + 2 * c] += w * f.x;
+            acc[h2 * 8 + 2 * c + 1] += w * f.y;
+          }
+        }
+      }
+      uint4 o[2];
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) oh[c] = __floats2bfloat162_rn(acc[2 * c], acc[2 * c + 1]);
+      uint4* dst = reinterpret_cast<uint4*>(out + t * D + col);
+      dst[0] = o[0];
+      dst[1] = o[1];
+    }
+    __syncwarp();      // everyone has read the buffer before it is requested again (two items later)
+  }
+  // after a failed wait: let the pieces that are still on their way land before the shared memory goes away
+  for (long long i = done; i < requested; ++i) mbar_wait(&bars[2 * warp + (i & 1)], (i >> 1) & 1, nullptr);
+}
+
 }  // namespace
 
 int f1_rs_adam_ag(const float* const* peer_grads, void* const* peer_params, uint64_t* const* peer_flags,
@@ -444,10 +630,32 @@ int ep_dispatch_push(const void* x, const int* idx, const int* counts, int* seg_
                      int cap, unsigned long long epoch, int num_ctas, cudaStream_t st) {
   if (D % 8 != 0 || ep < 1 || experts_local < 1 || k < 1 || k > 32) return -1;
   ep_prepare_kernel<<<1, 32, 0, st>>>(counts, seg_off, peer_meta, my_rank, ep, experts_local);
-  ep_dispatch_push_kernel<<<num_ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), idx, counts, seg_off, cursor,
-                                                    pos, reinterpret_cast<__nv_bfloat16* const*>(peer_recv),
-                                                    peer_flags, cta_counter, my_rank, ep, experts_local, T, D, k, cap,
-                                                    epoch);
+  // Rows can also leave through the bulk-copy engine (PIPER_F3_BULK_PUSH=1).  Measured on a B200 pair the
+  // plain-store kernel is slightly faster (peer writes top out near 400-430 GB/s either way), so it is the default.
+  static int use_bulk = -1;
+  if (use_bulk < 0) {
+    const char* env = getenv("PIPER_F3_BULK_PUSH");
+    use_bulk = (env != nullptr && env[0] == '1') ? 1 : 0;
+  }
+  const size_t smem = static_cast<size_t>(256 / 32) * 2 * D * 2;
+  if (use_bulk && smem <= 200 * 1024) {
+    static size_t configured = 0;
+    if (smem > configured) {
+      if (cudaFuncSetAttribute(ep_dispatch_push_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)) != cudaSuccess)
+        return -2;
+      configured = smem;
+    }
+    ep_dispatch_push_bulk_kernel<<<num_ctas, 256, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(x), idx, counts, seg_off, cursor, pos,
+        reinterpret_cast<__nv_bfloat16* const*>(peer_recv), peer_flags, cta_counter, my_rank, ep, experts_local, T, D,
+        k, cap, epoch);
+  } else {
+    ep_dispatch_push_kernel<<<num_ctas, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), idx, counts, seg_off,
+                                                      cursor, pos, reinterpret_cast<__nv_bfloat16* const*>(peer_recv),
+                                                      peer_flags, cta_counter, my_rank, ep, experts_local, T, D, k, cap,
+                                                      epoch);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -468,6 +676,27 @@ int ep_combine_pull(const void* const* peer_out, const int* pos, const float* we
                     const uint64_t* out_flags, long long T, int D, int k, int ep, int cap, unsigned long long epoch,
                     unsigned long long timeout_ns, int* status, int num_ctas, cudaStream_t st) {
   if (D % 8 != 0 || k < 1 || k > 32) return -1;
+  // Bulk loads into shared memory are the default: on a B200 pair they pull 530 GB/s against 485 GB/s for plain
+  // peer loads (PIPER_F3_BULK_PULL=0 selects the plain-load kernel).
+  static int use_bulk = -1;
+  if (use_bulk < 0) {
+    const char* env = getenv("PIPER_F3_BULK_PULL");
+    use_bulk = (env != nullptr && env[0] == '0') ? 0 : 1;
+  }
+  const size_t smem = static_cast<size_t>(256 / 32) * 2 * k * kPullChunk;
+  if (use_bulk && smem <= 200 * 1024) {
+    static size_t configured = 0;
+    if (smem > configured) {
+      if (cudaFuncSetAttribute(ep_combine_pull_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem)) != cudaSuccess)
+        return -2;
+      configured = smem;
+    }
+    ep_combine_pull_bulk_kernel<<<num_ctas, 256, smem, st>>>(
+        reinterpret_cast<const __nv_bfloat16* const*>(peer_out), pos, weights, static_cast<__nv_bfloat16*>(out),
+        out_flags, T, D, k, ep, cap, epoch, timeout_ns, status);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  }
   ep_combine_pull_kernel<<<num_ctas, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16* const*>(peer_out), pos,
                                                    weights, static_cast<__nv_bfloat16*>(out), out_flags, T, D, k, ep,
                                                    cap, epoch, timeout_ns, status);

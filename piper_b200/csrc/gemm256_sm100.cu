@@ -40,6 +40,8 @@ constexpr int MN_BOX_BYTES = 64 * BK * 2;
 constexpr int NUM_THREADS = 384;
 constexpr int EPI_WARPS = 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int C_STAGE_BYTES = 32 * 32 * 4;   // fp32 epilogue: one 32x32 block per epilogue warp
+constexpr int SMEM_BYTES_F32 = STAGES * STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers, padded*/ + EPI_WARPS * C_STAGE_BYTES;
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -54,8 +56,8 @@ struct Barriers {
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               void* __restrict__ c_ptr, long long ldc, int M, int N, int K, int accumulate, int* status,
-               int* sched) {
+               const __grid_constant__ CUtensorMap tmap_c, void* __restrict__ c_ptr, long long ldc, int M, int N,
+               int K, int accumulate, int* status, int* sched) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -241,28 +243,26 @@ gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 for (int j = 0; j < 32; ++j)   // constant indices keep r[] in registers
                   if (col0 + j < N) crow[j] = __float2bfloat16(__uint_as_float(r[j]));
               }
-            } else {
-              float* crow = reinterpret_cast<float*>(c_ptr) + row * ldc + col0;
-              if (col0 + 32 <= N) {
+            }
+          }
+          if (EPI == kEpiAccumF32 && m0 + h * 128 + q * 32 < M && col0 < N) {
+            // fp32 output: stage the warp's 32x32 block in shared memory (16-byte chunks XOR-swizzled by row) and
+            // send it as one TMA store, or one TMA reduce-add when accumulating (see gemm_sm100.cu)
+            float* cbuf = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 1024 + (warp - 4) * C_STAGE_BYTES);
+            bulk_wait_group_read<0>();               // the previous block has left the buffer
+            __syncwarp();
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                  float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
-                                         __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                  if (accumulate) {
-                    const float4 p = reinterpret_cast<const float4*>(crow)[v];
-                    o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                  }
-                  reinterpret_cast<float4*>(crow)[v] = o;
-                }
-              } else {
-                #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  if (col0 + j < N) {
-                    const float x = __uint_as_float(r[j]);
-                    crow[j] = accumulate ? crow[j] + x : x;
-                  }
-                }
-              }
+            for (int v = 0; v < 8; ++v) {
+              const float4 o = make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]),
+                                           __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+              reinterpret_cast<float4*>(cbuf + lane * 32)[v ^ (lane & 7)] = o;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (accumulate) tma_reduce_add_2d_bulk(&tmap_c, cbuf, col0, m0 + h * 128 + q * 32);
+              else tma_store_2d_bulk(&tmap_c, cbuf, col0, m0 + h * 128 + q * 32);
+              bulk_commit_group();
             }
           }
         }
@@ -271,6 +271,7 @@ gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (lane == 0) mbar_arrive(&bars->acc_empty[h]);   // the next tile may overwrite this half
       }
     }
+    if (EPI == kEpiAccumF32 && lane == 0) bulk_wait_group<0>();   // staged blocks must leave before the CTA does
   }
 
   tc_fence_before();
@@ -292,14 +293,21 @@ template <bool A_MN, bool B_MN, int EPI>
 int launch256(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& tb, int num_sms, int* sched,
               cudaStream_t stream) {
   auto kern = gemm256_kernel<A_MN, B_MN, EPI>;
+  constexpr int smem_bytes = EPI == kEpiAccumF32 ? SMEM_BYTES_F32 : SMEM_BYTES;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -2;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -2;
     configured = true;
+  }
+  CUtensorMap tc = ta;      // unused by the bf16 epilogue
+  if (EPI == kEpiAccumF32) {
+    const int rc = make_tmap_c_f32(&tc, g.c, g.N, g.M, static_cast<uint64_t>(g.ldc) * 4);
+    if (rc != 0) return rc;
   }
   const int tiles = ((g.M + BM - 1) / BM) * ((g.N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, g.c, g.ldc, g.M, g.N, g.K, g.accumulate, g.status, sched);
+  kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(ta, tb, tc, g.c, g.ldc, g.M, g.N, g.K, g.accumulate, g.status,
+                                                  sched);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -365,7 +365,7 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64
 }
 
 // fp32 tensor map of C with 32x32 boxes and 128-byte swizzle (epilogue staging layout).
-static int make_tmap_c_f32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes) {
+int make_tmap_c_f32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes) {
   EncodeFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   const cuuint64_t dims[2] = {cols, rows};
@@ -416,12 +416,12 @@ int gemm_bf16_launch(const GemmArgs& g, int num_sms, cudaStream_t stream) {
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
   {
     // 256x256 tiles move a third fewer operand bytes per flop.  Measured on B200: they win for bf16 outputs once
-    // there is at least one tile per SM; with the fp32 read-modify-write epilogue, whose exposed drain is twice
-    // as long, only for long contractions.
+    // there is at least one tile per SM, and for fp32 (weight-gradient) outputs that are at least as tall as
+    // wide; wide fp32 outputs do a little better with 128x256 tiles and their double-buffered accumulators.
     const int tile = g.tile != 0 ? g.tile : forced_tile();
     const long long tiles256 = static_cast<long long>((g.M + 255) / 256) * ((g.N + 255) / 256);
     const bool fits = g.M >= 256 && g.N >= 256 && tiles256 >= num_sms;
-    const bool pays = g.epilogue == kEpiStoreBf16 || g.K >= 8192;
+    const bool pays = g.epilogue == kEpiStoreBf16 || g.M >= g.N;
     if (tile == 256 || (tile == 0 && fits && pays))
       return gemm256_bf16_launch(g, num_sms, next_sched_slot(), stream);
   }

@@ -95,6 +95,9 @@ struct AgGemmArgs {
 
 int ag_gemm_launch(const AgGemmArgs& args, int num_sms, cudaStream_t stream);
 
+// fp32 tensor map of an output matrix with 32x32 boxes and 128-byte swizzle (layout of the fp32 epilogue staging).
+int make_tmap_c_f32(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes);
+
 // Encodes a 2-D bf16 tensor map with 128-byte swizzle.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer);

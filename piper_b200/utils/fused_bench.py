@@ -254,6 +254,24 @@ def main():
                      "fraction_of_roofline": roof / ms_d, "nvlink_GBs": nv / ms_d / 1e6})
         rows.append({"path": "F3 combine pull", "ctas": ctas, "world": world, "ms": ms_c, "roofline_ms": roof,
                      "fraction_of_roofline": roof / ms_c, "nvlink_GBs": nv / ms_c / 1e6})
+    # NCCL lowering of the same exchange, without its host-side count exchange: local permutation kernel +
+    # equal-split all_to_all of the routed rows, and all_to_all + local weighted combine on the way back
+    routed = T * k // world * world
+    a2a_in = torch.empty((routed, D), dtype=torch.bfloat16, device=dev)
+    a2a_out = torch.empty_like(a2a_in)
+
+    def nccl_dispatch():
+        rws, _p, _gs, _gl, _c = M.moe_dispatch(xt, idx, counts)
+        dist.all_to_all_single(a2a_out, rws[:routed])
+
+    local = M.moe_dispatch(xt, idx, counts)
+
+    def nccl_combine():
+        dist.all_to_all_single(a2a_in, a2a_out)
+        M.moe_combine(local[0], local[1], weights, local[2], local[3], counts)
+
+    rows.append({"path": "NCCL dispatch: permute kernel + all_to_all_single", "world": world, "ms": _median_ms(nccl_dispatch)})
+    rows.append({"path": "NCCL combine: all_to_all_single + combine kernel", "world": world, "ms": _median_ms(nccl_combine)})
     native.check_status()
     if rank == 0:
         for r in rows:

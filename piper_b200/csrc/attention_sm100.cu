@@ -307,12 +307,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       }
       tc_fence_before();
       warp_arrive(&bars->s_empty[s], lane);            // the scores live in registers from here on
+      if (diag) {
+        // causal mask, applied once to the registers of the only tile that needs it: a score of -inf then
+        // drops out of the maximum and turns into a probability of exactly zero below
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (wg * 64 + i > row) sv[i] = 0xff800000u;
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float v = (diag && (wg * 64 + i) > row) ? -INFINITY : __uint_as_float(sv[i]);
-        mx = fmaxf(mx, v);
-      }
+      for (int i = 0; i < 64; i += 2)
+        mx = fmaxf(mx, fmaxf(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])));
       xbuf[(s * 2 + wg) * 128 + row] = mx;
       warp_arrive(&bars->mx_full[s], lane);
       if (!await_all(&bars->mx_full[s], (j >> 1) & 1, status)) { ok = false; break; }
@@ -327,10 +332,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = fast_exp2(__uint_as_float(sv[c * 32 + 2 * i]) * scale_log2 - msc);
-          float p1 = fast_exp2(__uint_as_float(sv[c * 32 + 2 * i + 1]) * scale_log2 - msc);
-          if (diag && (wg * 64 + c * 32 + 2 * i) > row) p0 = 0.f;
-          if (diag && (wg * 64 + c * 32 + 2 * i + 1) > row) p1 = 0.f;
+          const float p0 = fast_exp2(__uint_as_float(sv[c * 32 + 2 * i]) * scale_log2 - msc);
+          const float p1 = fast_exp2(__uint_as_float(sv[c * 32 + 2 * i + 1]) * scale_log2 - msc);
           rs += p0 + p1;
           w[i] = pack_bf16x2(p0, p1);
         }
@@ -711,6 +714,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         tmem_ld_wait();
         tc_fence_before();
         warp_arrive(&bars->s_empty[st], lane);   // S'/dP' of this stage now live in registers
+        if (need_mask) {
+          // causal mask, applied once to the registers of the tiles that cross the diagonal: a score of -inf
+          // turns into a probability (and a score gradient) of exactly zero below
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            const int qpos = (MODE == 0) ? xpos : ypos0 + col;
+            const int kpos = (MODE == 0) ? ypos0 + col : xpos;
+            if (kpos > qpos) sv[i] = 0xff800000u;
+          }
+        }
         uint32_t pw[16], dw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -720,12 +734,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
             const int col = c * 32 + 2 * i + e;
             const float l2 = (MODE == 0) ? row_lse : vec[vs * 128 + col];
             const float dl = (MODE == 0) ? row_delta : vec[vs * 128 + 64 + col];
-            float pv = fast_exp2(__uint_as_float(sv[2 * i + e]) * scale_log2 - l2);
-            if (need_mask) {
-              const int qpos = (MODE == 0) ? xpos : ypos0 + col;
-              const int kpos = (MODE == 0) ? ypos0 + col : xpos;
-              if (kpos > qpos) pv = 0.f;
-            }
+            const float pv = fast_exp2(__uint_as_float(sv[2 * i + e]) * scale_log2 - l2);
             p[e] = pv;
             d[e] = pv * (__uint_as_float(dv[2 * i + e]) - dl);
           }

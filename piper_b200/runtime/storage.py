@@ -24,6 +24,7 @@ single-process model start from identical weights.
 """
 from __future__ import annotations
 
+import os
 import zlib
 from dataclasses import dataclass, field
 from typing import Any, Callable, Optional
@@ -33,6 +34,9 @@ import torch.distributed as dist
 
 from ..ops import core as ops_core
 from ..ops import native
+
+# PIPER_DEBUG_POISON=1: fill gathered ZeRO-3 parameters with NaN right before their storage is released
+_POISON_FREED = os.environ.get("PIPER_DEBUG_POISON", "0") == "1"
 
 ALIGN = 64  # elements; keeps every parameter view 128-byte aligned in bf16
 
@@ -206,6 +210,10 @@ class ParamStorage:
         self._unregister_sinks()
         if consumer_stream is not None and self.flat_params.is_cuda:
             self.flat_params.record_stream(consumer_stream)
+        if _POISON_FREED:
+            # debug aid: a kernel that still reads these parameters after the free (a missing event or a wrong
+            # ZeRO lifetime in the plan) then produces NaNs instead of silently using stale weights
+            self.flat_params.fill_(float("nan"))
         self.flat_params.untyped_storage().resize_(0)
         self.params_live = False
 

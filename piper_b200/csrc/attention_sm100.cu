@@ -39,6 +39,19 @@ namespace {
 // 0: waits suspend inside mbarrier.try_wait; 1: waits poll mbarrier.test_wait (set from PIPER_ATTN_SPIN).
 __constant__ int c_attn_spin;
 
+// Optional timeline of one CTA of the backward kernels (a debugging aid, off unless attn_set_trace installs a
+// buffer of 16 * 256 timestamps): event kind k of iteration it, written by block (0, 0, 0) only.
+__device__ unsigned long long* g_attn_trace;
+
+__device__ __forceinline__ void trace_event(int kind, int it) {
+  unsigned long long* t = g_attn_trace;
+  if (t != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && it < 256) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    t[kind * 256 + it] = now;
+  }
+}
+
 // Bounded wait on an mbarrier phase (see mbar_wait in ptx.cuh), in either of the two forms above.
 __device__ __forceinline__ bool await(uint64_t* bar, uint32_t parity, int* status) {
   if (c_attn_spin == 0) return mbar_wait(bar, parity, status);
@@ -219,6 +232,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, HD, false, true);
       const uint32_t q_addr = smem_u32(smem + L::Q_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
+      // descriptors of the operands that never move (Q, the probability tile), one per k-step: the issuing
+      // thread's instruction count per MMA is what bounds the loops below
+      uint64_t dq[HD / 16], dp[8];
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks)
+        dq[ks] = umma_desc_sw128(q_addr + (ks / 4) * 16384 + (ks % 4) * 32, 16, 1024);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        dp[ks] = umma_desc_sw128(p_addr + (ks / 4) * 16384 + (ks % 4) * 32, 16, 1024);
       bool ok = await(&bars->q_full, 0, status);
       // Two queues served in whatever order their inputs arrive: S of block s_next (needs K and a free TMEM
       // stage) and P V of block p_next (needs the probabilities, V and a free output stage).
@@ -232,14 +254,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
           if (mbar_test_wait(&bars->p_full, jj & 1) && mbar_test_wait(&bars->v_full[sb], (jj >> 1) & 1) &&
               mbar_test_wait(&bars->o_empty[sb], ((jj >> 1) & 1) ^ 1)) {
             tc_fence_after();
-            const uint32_t v_addr = smem_u32(smem + L::V_OFF + sb * L::TILE);
+            const uint64_t dv0 = umma_desc_sw128(smem_u32(smem + L::V_OFF + sb * L::TILE), 16384, 1024);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
-              umma_bf16_ss(tmem_o + sb * HD, umma_desc_sw128(p_addr + a_off, 16, 1024),
-                           umma_desc_sw128(v_addr + ks * 2048, 16384, 1024), idesc_pv,
-                           ks > 0 ? 1u : 0u);
-            }
+            for (int ks = 0; ks < 8; ++ks)
+              umma_bf16_ss(tmem_o + sb * HD, dp[ks], dv0 + (ks * 2048 >> 4), idesc_pv, ks > 0 ? 1u : 0u);
             umma_commit(&bars->p_empty);
             umma_commit(&bars->o_full[sb]);
             umma_commit(&bars->v_empty[sb]);
@@ -253,12 +271,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap, __nv_bfloat16* __restr
           if (mbar_test_wait(&bars->k_full[s], (j >> 1) & 1) &&
               mbar_test_wait(&bars->s_empty[s], ((j >> 1) & 1) ^ 1)) {
             tc_fence_after();
-            const uint32_t k_addr = smem_u32(smem + L::K_OFF + s * L::TILE);
+            const uint64_t dk0 = umma_desc_sw128(smem_u32(smem + L::K_OFF + s * L::TILE), 16, 1024);
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
               const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-              umma_bf16_ss(tmem_s + s * 128, umma_desc_sw128(q_addr + off, 16, 1024),
-                           umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+              umma_bf16_ss(tmem_s + s * 128, dq[ks], dk0 + (off >> 4), idesc_qk, ks > 0 ? 1u : 0u);
             }
             umma_commit(&bars->s_full[s]);
             umma_commit(&bars->k_empty[s]);
@@ -443,18 +460,26 @@ struct BwdSmem {
   static constexpr int PT_BYTES = 128 * 64 * 2;    // P' or dS' tile (one swizzle row per row)
   static constexpr int X1_OFF = 0;
   static constexpr int X2_OFF = X_TILE;
-  static constexpr int Y_STAGES = 3;
-  static constexpr int Y_OFF = 2 * X_TILE;         // Y_STAGES x (Y1, Y2)
+  static constexpr int Y_STAGES = 4;
+  static constexpr int Y_OFF = 2 * X_TILE;         // Y_STAGES x (Y1, Y2), see y_off
+  // Streamed stages are laid out in pairs: the same 64-column half of the same operand of stages 2p and 2p+1
+  // is one contiguous 128-row tile.  (Issuing S' and dP' of two consecutive tiles as one N = 128 MMA each was
+  // tried on this layout: every MMA costs the issuing thread about 110 cycles whatever its width, but the two
+  // TMEM stages are never free at the same moment in steady state, so the pairs did not form.)
+  static constexpr int HALF_STRIDE = 2 * Y_HALF;   // between the 64-column halves of one stage's operand
+  __host__ __device__ static constexpr int y_off(int st, int operand, int half) {
+    return (st >> 1) * (4 * Y_TILE) + operand * (2 * Y_TILE) + half * HALF_STRIDE + (st & 1) * Y_HALF;
+  }
   static constexpr int P_OFF = Y_OFF + Y_STAGES * 2 * Y_TILE;
   static constexpr int DS_OFF = P_OFF + PT_BYTES;
-  static constexpr int VEC_OFF = DS_OFF + PT_BYTES;      // 4 stages x (lse[64], delta[64]) floats
-  static constexpr int BAR_OFF = VEC_OFF + 4 * 2 * 64 * 4;
+  static constexpr int VEC_OFF = DS_OFF + PT_BYTES;              // 3 stages x (lse[64], delta[64]) floats
+  static constexpr int BAR_OFF = VEC_OFF + 3 * 2 * 64 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
 struct BwdBars {
   uint64_t x_full;
-  uint64_t y_full[3], y_empty[3];     // streamed tiles (BwdSmem::Y_STAGES)
+  uint64_t y_full[4], y_empty[4];     // streamed tiles (BwdSmem::Y_STAGES)
   uint64_t s_full[2], s_empty[2];     // S' and dP' pair
   uint64_t t_full, t_empty;           // P'/dS' shared-memory tiles
   uint64_t v_full[2];                 // per-column lse/delta vectors (MODE 1)
@@ -523,7 +548,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
-  // columns: [0,64) S'0  [64,128) dP'0  [128,192) S'1  [192,256) dP'1
+  // columns: [0,64) S'0  [64,128) S'1  [128,192) dP'0  [192,256) dP'1
   //          [256,256+HD) acc1   [384,384+HD) acc2
   const uint32_t tmem_acc1 = tmem_base + 256;
   const uint32_t tmem_acc2 = tmem_base + 384;
@@ -551,17 +576,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         const int hh = (MODE == 0) ? hy : g * group + it / tiles_per_head;   // query head
         const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;      // streamed tile index
         const int yrow = static_cast<int>(tok0) + ti * 64;
-        uint8_t* y1 = smem + L::Y_OFF + st * 2 * L::Y_TILE;
-        uint8_t* y2 = y1 + L::Y_TILE;
+        uint8_t* yb = smem + L::Y_OFF;
+        trace_event(8 * MODE + 0, it);               // streamed tile requested
         mbar_arrive_expect_tx(&bars->y_full[st], 2 * L::Y_TILE);
         for (int h = 0; h < L::HALVES; ++h) {
+          uint8_t* y1 = yb + L::y_off(st, 0, h);
+          uint8_t* y2 = yb + L::y_off(st, 1, h);
           if (MODE == 0) {
-            tma_load_2d(y1 + h * L::Y_HALF, &tmap_qkv_y, &bars->y_full[st], (Hq + g) * HD + 64 * h, yrow);
-            tma_load_2d(y2 + h * L::Y_HALF, &tmap_qkv_y, &bars->y_full[st],
-                        (Hq + Hkv + g) * HD + 64 * h, yrow);
+            tma_load_2d(y1, &tmap_qkv_y, &bars->y_full[st], (Hq + g) * HD + 64 * h, yrow);
+            tma_load_2d(y2, &tmap_qkv_y, &bars->y_full[st], (Hq + Hkv + g) * HD + 64 * h, yrow);
           } else {
-            tma_load_2d(y1 + h * L::Y_HALF, &tmap_qkv_y, &bars->y_full[st], hh * HD + 64 * h, yrow);
-            tma_load_2d(y2 + h * L::Y_HALF, &tmap_do_y, &bars->y_full[st], hh * HD + 64 * h, yrow);
+            tma_load_2d(y1, &tmap_qkv_y, &bars->y_full[st], hh * HD + 64 * h, yrow);
+            tma_load_2d(y2, &tmap_do_y, &bars->y_full[st], hh * HD + 64 * h, yrow);
           }
         }
       }
@@ -581,6 +607,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
       const uint32_t x2 = smem_u32(smem + L::X2_OFF);
       const uint32_t p_addr = smem_u32(smem + L::P_OFF);
       const uint32_t ds_addr = smem_u32(smem + L::DS_OFF);
+      uint64_t dx1[HD / 16], dx2[HD / 16];       // descriptors of the stationary operands, fixed for the kernel
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
+        dx1[ks] = umma_desc_sw128(x1 + xo, 16, 1024);
+        dx2[ks] = umma_desc_sw128(x2 + xo, 16, 1024);
+      }
+      const uint64_t d_ds = umma_desc_sw128(ds_addr, 16, 1024);
+      const uint64_t d_p = umma_desc_sw128(p_addr, 16, 1024);
       bool ok = await(&bars->x_full, 0, status);
       // Two queues served in whatever order their inputs arrive: S'/dP' of tile s_next needs its streamed tile
       // and a free TMEM stage; the accumulation of tile a_next needs the P'/dS' tiles the threads wrote.  A fixed
@@ -593,20 +628,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         if (a_next < s_next && mbar_test_wait(&bars->t_full, a_next & 1)) {
           const int jt = a_next;
           const int st = jt % L::Y_STAGES;
+          trace_event(8 * MODE + 2, jt);             // accumulation MMAs issued
           tc_fence_after();
-          const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
-          const uint32_t y2 = y1 + L::Y_TILE;
+          const uint64_t dy1 = umma_desc_sw128(smem_u32(smem + L::Y_OFF + L::y_off(st, 0, 0)), L::HALF_STRIDE, 1024);
+          const uint64_t dy2 = umma_desc_sw128(smem_u32(smem + L::Y_OFF + L::y_off(st, 1, 0)), L::HALF_STRIDE, 1024);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {   // contraction over the 64 streamed rows
-            umma_bf16_ss(tmem_acc1, umma_desc_sw128(ds_addr + ks * 32, 16, 1024),
-                         umma_desc_sw128(y1 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
+            umma_bf16_ss(tmem_acc1, d_ds + (ks * 32 >> 4), dy1 + (ks * 2048 >> 4), idesc_acc,
                          (jt > 0 || ks > 0) ? 1u : 0u);
           }
           if (MODE == 1) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-              umma_bf16_ss(tmem_acc2, umma_desc_sw128(p_addr + ks * 32, 16, 1024),
-                           umma_desc_sw128(y2 + ks * 2048, L::Y_HALF, 1024), idesc_acc,
+              umma_bf16_ss(tmem_acc2, d_p + (ks * 32 >> 4), dy2 + (ks * 2048 >> 4), idesc_acc,
                            (jt > 0 || ks > 0) ? 1u : 0u);
             }
           }
@@ -622,22 +656,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           const int ss = it & 1;
           if (mbar_test_wait(&bars->y_full[st], (it / L::Y_STAGES) & 1) &&
               mbar_test_wait(&bars->s_empty[ss], ((it >> 1) & 1) ^ 1)) {
+            trace_event(8 * MODE + 1, it);           // S'/dP' MMAs issued
             tc_fence_after();
-            const uint32_t y1 = smem_u32(smem + L::Y_OFF + st * 2 * L::Y_TILE);
-            const uint32_t y2 = y1 + L::Y_TILE;
+            const uint32_t y1 = smem_u32(smem + L::Y_OFF + L::y_off(st, 0, 0));
+            const uint32_t y2 = smem_u32(smem + L::Y_OFF + L::y_off(st, 1, 0));
+            constexpr uint32_t idesc = idesc_s;
+            // one descriptor per operand and tile; the k-steps only add a constant to its address field (the
+            // issuing thread's instruction count per MMA is what bounds this loop)
+            const uint64_t dy1 = umma_desc_sw128(y1, 16, 1024);
+            const uint64_t dy2 = umma_desc_sw128(y2, 16, 1024);
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
-              const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
-              const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
-              umma_bf16_ss(tmem_base + ss * 128, umma_desc_sw128(x1 + xo, 16, 1024),
-                           umma_desc_sw128(y1 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+              const uint32_t yo = (ks / 4) * L::HALF_STRIDE + (ks % 4) * 32;
+              umma_bf16_ss(tmem_base + ss * 64, dx1[ks], dy1 + (yo >> 4), idesc, ks > 0 ? 1u : 0u);
             }
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
-              const uint32_t xo = (ks / 4) * 16384 + (ks % 4) * 32;
-              const uint32_t yo = (ks / 4) * L::Y_HALF + (ks % 4) * 32;
-              umma_bf16_ss(tmem_base + ss * 128 + 64, umma_desc_sw128(x2 + xo, 16, 1024),
-                           umma_desc_sw128(y2 + yo, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+              const uint32_t yo = (ks / 4) * L::HALF_STRIDE + (ks % 4) * 32;
+              umma_bf16_ss(tmem_base + 128 + ss * 64, dx2[ks], dy2 + (yo >> 4), idesc, ks > 0 ? 1u : 0u);
             }
             umma_commit(&bars->s_full[ss]);
             ++s_next;
@@ -670,29 +706,29 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
     float pre_lse = 0.f, pre_delta = 0.f;      // MODE 1: this thread's lse/delta entries of the next streamed tile
     if (MODE == 1 && wg == 0 && row < 64 && n_iter > 0) {
       const long long idx = (static_cast<long long>(b) * Hq + g * group) * S + 2 * xb * 64 + row;
-      pre_lse = lse[idx] * 1.4426950408889634f;
+      pre_lse = lse[idx];
       pre_delta = delta[idx];
     }
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int st = it & 1;
-      // lse/delta vectors: four stages, so a stage is rewritten only after every thread has left the
+      // lse/delta vectors: three stages, so a stage is rewritten only after every thread has left the
       // iteration that read it (a thread enters iteration it only after the MMAs of it - 2 have retired)
-      const int vs = it & 3;
+      const int vs = it % 3;
       const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;
       if (MODE == 1) {
         // Per-column lse/delta of the streamed query tile -> shared memory.  The values of the next tile are
         // requested right away and stay in flight while this tile is processed.
         if (wg == 0 && row < 64) {
-          vec[vs * 128 + row] = pre_lse;
+          vec[vs * 128 + row] = pre_lse * 1.4426950408889634f;
           vec[vs * 128 + 64 + row] = pre_delta;
           warp_arrive(&bars->v_full[st], lane);
           if (it + 1 < n_iter) {
             const int hn = g * group + (it + 1) / tiles_per_head;
             const int tn = 2 * xb + (it + 1) % tiles_per_head;
             const long long idx = (static_cast<long long>(b) * Hq + hn) * S + tn * 64 + row;
-            pre_lse = lse[idx] * 1.4426950408889634f;
-            pre_delta = delta[idx];
+            pre_lse = lse[idx];            // no arithmetic on these until the next iteration: a dependent
+            pre_delta = delta[idx];        // instruction here would stall this warp on the loads right away
           }
         }
         // Bounded wait instead of a named barrier: a thread that gave up on
@@ -700,17 +736,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         if (!await_all(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       }
       if (!await_all(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
+      if (threadIdx.x == 0) trace_event(8 * MODE + 3, it);     // S'/dP' seen complete
       tc_fence_after();
       // Causal mask is needed only where the streamed tile overlaps the
       // stationary rows: element (x row, y col) is kept iff key <= query.
       const int ypos0 = ti * 64;
       const bool need_mask = (MODE == 0) ? (ypos0 + 63 > xb * 128) : (ypos0 < xb * 128 + 127);
-      const uint32_t ts = tmem_base + lane_sel + st * 128;
+      const uint32_t ts = tmem_base + lane_sel + st * 64;
       {
         const int c = wg;
         uint32_t sv[32], dv[32];
         tmem_ld_32x32(ts + c * 32, sv);
-        tmem_ld_32x32(ts + 64 + c * 32, dv);
+        tmem_ld_32x32(ts + 128 + c * 32, dv);
         tmem_ld_wait();
         tc_fence_before();
         warp_arrive(&bars->s_empty[st], lane);   // S'/dP' of this stage now live in registers
@@ -741,13 +778,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           pw[i] = pack_bf16x2(p[0], p[1]);
           dw[i] = pack_bf16x2(d[0], d[1]);
         }
+        if (threadIdx.x == 0) trace_event(8 * MODE + 4, it);   // P'/dS' computed
         // the tiles were last read by the MMAs of the previous iteration
         if (it >= 1 && !await_all(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
+        if (threadIdx.x == 0) trace_event(8 * MODE + 5, it);   // tile buffer free
         if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
         store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
       }
       fence_proxy_async_smem();
       warp_arrive(&bars->t_full, lane);
+      if (threadIdx.x == 0) trace_event(8 * MODE + 6, it);     // P'/dS' published
     }
     if (ok && await_all(&bars->acc_full, 0, status)) {
       tc_fence_after();
@@ -865,6 +905,10 @@ static int attn_bwd_impl(const void* qkv, const void* out, const void* d_out, co
       tqx, tqy, tdx, tdy, lse, delta, static_cast<__nv_bfloat16*>(d_qkv), S, Hq, Hkv, softmax_scale,
       scale_log2, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int attn_set_trace(unsigned long long* buf) {
+  return cudaMemcpyToSymbol(g_attn_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
 }
 
 int attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,

@@ -184,12 +184,13 @@ gemm256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             const uint32_t tmem_d = tmem_base + h * BN;
             const uint32_t sah = A_MN ? sa + h * 2 * MN_BOX_BYTES : sa + h * A_HALF_BYTES;
+            // one descriptor per operand; a k-step only adds a constant to its address field
+            const uint64_t da0 = A_MN ? umma_desc_sw128(sah, MN_BOX_BYTES, 1024) : umma_desc_sw128(sah, 16, 1024);
+            const uint64_t db0 = B_MN ? umma_desc_sw128(sb, MN_BOX_BYTES, 1024) : umma_desc_sw128(sb, 16, 1024);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t da = A_MN ? umma_desc_sw128(sah + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
-                                       : umma_desc_sw128(sah + k * (UMMA_K * 2), 16, 1024);
-              const uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
-                                       : umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+              const uint64_t da = da0 + ((A_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2)) >> 4);
+              const uint64_t db = db0 + ((B_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2)) >> 4);
               umma_bf16_ss(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
           }

@@ -188,12 +188,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
+          // one descriptor per operand and stage; a k-step only adds a constant to its address field, which
+          // keeps the issuing thread's instruction count per MMA low
+          const uint64_t da0 = A_MN ? umma_desc_sw128(sa, MN_BOX_BYTES, 1024) : umma_desc_sw128(sa, 16, 1024);
+          const uint64_t db0 = B_MN ? umma_desc_sw128(sb, MN_BOX_BYTES, 1024) : umma_desc_sw128(sb, 16, 1024);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = A_MN ? umma_desc_sw128(sa + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
-                                     : umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
-            const uint64_t db = B_MN ? umma_desc_sw128(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024)
-                                     : umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t da = da0 + ((A_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2)) >> 4);
+            const uint64_t db = db0 + ((B_MN ? k * (UMMA_K * 128) : k * (UMMA_K * 2)) >> 4);
             umma_bf16_ss(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&bars->empty[s]);       // frees the smem stage when the MMAs retire

@@ -180,15 +180,169 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int i = threadIdx.x; i < D; i += NORM_THREADS) out[i] = dw_acc[i];
 }
 
+// Register-resident variants for D == VPT * 8 * NORM_THREADS (2048, 4096, 8192): every thread owns VPT
+// 8-element vectors of the row, so the row is read from memory exactly once and the block reduction needs a
+// single barrier (the per-warp sums alternate between two scratch rows; a thread can only reach the write of
+// row k+2 after every thread has passed the barrier of row k+1, i.e. after all reads of row k).
+__device__ __forceinline__ float block_sum_once(float v, float (*scratch)[NORM_THREADS / 32], int parity) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) scratch[parity][threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_THREADS / 32; ++i) t += scratch[parity][i];
+  return t;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                       __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd, float eps) {
+  constexpr int D = VPT * 8 * NORM_THREADS;
+  __shared__ float scratch[2][NORM_THREADS / 32];
+  const long long row = blockIdx.x;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * D);
+  bf16x8 xv[VPT], rv[VPT];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) xv[v] = xr[threadIdx.x + v * NORM_THREADS];
+  if (res) {
+    const bf16x8* rr = reinterpret_cast<const bf16x8*>(res + row * D);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) rv[v] = rr[threadIdx.x + v * NORM_THREADS];
+  }
+  float f[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    unpack8(xv[v], f[v]);
+    if (res) {
+      float g[8];
+      unpack8(rv[v], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[v][j] += g[j];
+      const bf16x8 hp = pack8(f[v]);   // the residual stream is bf16: normalise what is stored
+      reinterpret_cast<bf16x8*>(h_out + row * D)[threadIdx.x + v * NORM_THREADS] = hp;
+      unpack8(hp, f[v]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += f[v][j] * f[v][j];
+  }
+  ss = block_sum_once(ss, scratch, 0);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0) rstd[row] = r;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * D);
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    float g[8];
+    unpack8(wr[threadIdx.x + v * NORM_THREADS], g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[v][j] = f[v][j] * r * g[j];
+    yr[threadIdx.x + v * NORM_THREADS] = pack8(f[v]);
+  }
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                       const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                       float* __restrict__ dw_partial, int T) {
+  constexpr int D = VPT * 8 * NORM_THREADS;
+  __shared__ float scratch[2][NORM_THREADS / 32];
+  float g[VPT][8], dw[VPT][8];
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    unpack8(reinterpret_cast<const bf16x8*>(w)[threadIdx.x + v * NORM_THREADS], g[v]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dw[v][j] = 0.f;
+  }
+  // The next row's vectors are fetched before the current row is reduced, so the loads overlap the barrier.
+  bf16x8 na[VPT], nb[VPT], ne[VPT];
+  float nr = 0.f;
+  long long row = blockIdx.x;
+  auto fetch = [&](long long rw) {
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + rw * D);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + rw * D);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      na[v] = dyr[threadIdx.x + v * NORM_THREADS];
+      nb[v] = xr[threadIdx.x + v * NORM_THREADS];
+    }
+    if (dres) {
+      const bf16x8* er = reinterpret_cast<const bf16x8*>(dres + rw * D);
+#pragma unroll
+      for (int v = 0; v < VPT; ++v) ne[v] = er[threadIdx.x + v * NORM_THREADS];
+    }
+    nr = rstd[rw];
+  };
+  if (row < T) fetch(row);
+  int parity = 0;
+  for (; row < T; row += gridDim.x, parity ^= 1) {
+    float a[VPT][8], b[VPT][8], e[VPT][8];
+    const float r = nr;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      unpack8(na[v], a[v]);
+      unpack8(nb[v], b[v]);
+      if (dres) unpack8(ne[v], e[v]);
+    }
+    if (row + gridDim.x < T) fetch(row + gridDim.x);
+    float dot = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        b[v][j] *= r;                       // xhat
+        dot += a[v][j] * g[v][j] * b[v][j];
+      }
+    dot = block_sum_once(dot, scratch, parity) / D;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = r * (a[v][j] * g[v][j] - b[v][j] * dot);
+        dw[v][j] += a[v][j] * b[v][j];
+        if (dres) o[j] += e[v][j];
+      }
+      dxr[threadIdx.x + v * NORM_THREADS] = pack8(o);
+    }
+  }
+  float* out = dw_partial + static_cast<long long>(blockIdx.x) * D;
+#pragma unroll
+  for (int v = 0; v < VPT; ++v) {
+    float4* o4 = reinterpret_cast<float4*>(out + (threadIdx.x + v * NORM_THREADS) * 8);
+    o4[0] = make_float4(dw[v][0], dw[v][1], dw[v][2], dw[v][3]);
+    o4[1] = make_float4(dw[v][4], dw[v][5], dw[v][6], dw[v][7]);
+  }
+}
+
 // dw[c] (+)= sum_b partial[b][c]; fp32 output (the flat gradient bucket) or
-// bf16 when dw_is_bf16.
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int D,
-                                       float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
-                                       int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+// bf16 when dw_bf16 is given.  A block owns 32 columns; its 8 thread rows each
+// sum a contiguous slice of the partials and the slices are added in a fixed
+// order, so the result does not depend on timing.
+constexpr int RED_SLICES = 8;
+__global__ void __launch_bounds__(32 * RED_SLICES)
+reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int D,
+                       float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
+                       int accumulate) {
+  __shared__ float part[RED_SLICES][32];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int per = (nblocks + RED_SLICES - 1) / RED_SLICES;
+  const int b0 = threadIdx.y * per;
+  const int b1 = min(nblocks, b0 + per);
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[static_cast<long long>(b) * D + c];
+  if (c < D)
+    for (int b = b0; b < b1; ++b) s += partial[static_cast<long long>(b) * D + c];
+  part[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y != 0 || c >= D) return;
+  s = 0.f;
+#pragma unroll
+  for (int i = 0; i < RED_SLICES; ++i) s += part[i][threadIdx.x];
   if (dw_f32) dw_f32[c] = accumulate ? dw_f32[c] + s : s;
   if (dw_bf16) dw_bf16[c] = __float2bfloat16(accumulate ? __bfloat162float(dw_bf16[c]) + s : s);
 }
@@ -538,6 +692,18 @@ int rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_
                 long long T, int D, float eps, cudaStream_t st) {
   if (D % 8 != 0) return -1;
   if (T == 0) return 0;
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* rp = static_cast<const __nv_bfloat16*>(res);
+  const auto* wp = static_cast<const __nv_bfloat16*>(w);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  auto* hp = static_cast<__nv_bfloat16*>(h_out);
+  const unsigned grid = static_cast<unsigned>(T);
+  switch (D) {
+    case 2048: rmsnorm_fwd_reg_kernel<1><<<grid, NORM_THREADS, 0, st>>>(xp, rp, wp, yp, hp, rstd, eps); return PIPER_LAUNCH_OK();
+    case 4096: rmsnorm_fwd_reg_kernel<2><<<grid, NORM_THREADS, 0, st>>>(xp, rp, wp, yp, hp, rstd, eps); return PIPER_LAUNCH_OK();
+    case 8192: rmsnorm_fwd_reg_kernel<4><<<grid, NORM_THREADS, 0, st>>>(xp, rp, wp, yp, hp, rstd, eps); return PIPER_LAUNCH_OK();
+    default: break;
+  }
   rmsnorm_fwd_kernel<<<static_cast<unsigned>(T), NORM_THREADS, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
@@ -556,6 +722,21 @@ int rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
   if (D % 8 != 0 || D * sizeof(float) > 160 * 1024) return -1;
   if (T == 0) return 0;
   const int nb = rmsnorm_bwd_num_partials(T);
+  const dim3 red_grid((D + 31) / 32), red_block(32, RED_SLICES);
+  if (D == 2048 || D == 4096 || D == 8192) {
+    const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
+    const auto* xp = static_cast<const __nv_bfloat16*>(x);
+    const auto* wp = static_cast<const __nv_bfloat16*>(w);
+    const auto* ep = static_cast<const __nv_bfloat16*>(dres);
+    auto* dxp = static_cast<__nv_bfloat16*>(dx);
+    const int Ti = static_cast<int>(T);
+    if (D == 2048) rmsnorm_bwd_reg_kernel<1><<<nb, NORM_THREADS, 0, st>>>(dyp, xp, wp, rstd, ep, dxp, dw_partial, Ti);
+    else if (D == 4096) rmsnorm_bwd_reg_kernel<2><<<nb, NORM_THREADS, 0, st>>>(dyp, xp, wp, rstd, ep, dxp, dw_partial, Ti);
+    else rmsnorm_bwd_reg_kernel<4><<<nb, NORM_THREADS, 0, st>>>(dyp, xp, wp, rstd, ep, dxp, dw_partial, Ti);
+    reduce_partials_kernel<<<red_grid, red_block, 0, st>>>(dw_partial, nb, D, dw_f32,
+                                                           static_cast<__nv_bfloat16*>(dw_bf16), accumulate);
+    return PIPER_LAUNCH_OK();
+  }
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -565,7 +746,7 @@ int rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
       static_cast<__nv_bfloat16*>(dx), dw_partial, static_cast<int>(T), D);
-  reduce_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, nb, D, dw_f32,
+  reduce_partials_kernel<<<red_grid, red_block, 0, st>>>(dw_partial, nb, D, dw_f32,
                                                          static_cast<__nv_bfloat16*>(dw_bf16), accumulate);
   return PIPER_LAUNCH_OK();
 }

@@ -106,13 +106,13 @@ def test_linear_op_autograd():
     assert _rel_err(w.grad, wr.grad) < 1e-2
 
 
-@pytest.mark.parametrize("D", [256, 2048, 4096])
-def test_rmsnorm_and_residual(D):
+@pytest.mark.parametrize("T,D", [(300, 256), (300, 2048), (1000, 4096), (300, 8192), (7, 4096)])
+def test_rmsnorm_and_residual(T, D):
     from piper_b200 import ops
 
     torch.manual_seed(3)
-    x = torch.randn(300, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    r = torch.randn(300, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     w = torch.randn(D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     y, h = ops.add_rmsnorm(x, r, w, 1e-6)
     gy, gh = torch.randn_like(y), torch.randn_like(h)

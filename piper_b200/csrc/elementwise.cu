@@ -243,18 +243,21 @@ rmsnorm_fwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
   }
 }
 
+// Two CTAs per SM (one for 8192-wide rows): the row vectors stay packed (bf16) in registers and are unpacked where they are used, which
+// keeps the kernel under 128 registers with the next row's loads in flight.
 template <int VPT>
-__global__ void __launch_bounds__(NORM_THREADS)
+__global__ void __launch_bounds__(NORM_THREADS, VPT <= 2 ? 2 : 1)
 rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                        float* __restrict__ dw_partial, int T) {
   constexpr int D = VPT * 8 * NORM_THREADS;
   __shared__ float scratch[2][NORM_THREADS / 32];
-  float g[VPT][8], dw[VPT][8];
+  bf16x8 gw[VPT];
+  float dw[VPT][8];
 #pragma unroll
   for (int v = 0; v < VPT; ++v) {
-    unpack8(reinterpret_cast<const bf16x8*>(w)[threadIdx.x + v * NORM_THREADS], g[v]);
+    gw[v] = reinterpret_cast<const bf16x8*>(w)[threadIdx.x + v * NORM_THREADS];
 #pragma unroll
     for (int j = 0; j < 8; ++j) dw[v][j] = 0.f;
   }
@@ -280,33 +283,44 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
   if (row < T) fetch(row);
   int parity = 0;
   for (; row < T; row += gridDim.x, parity ^= 1) {
-    float a[VPT][8], b[VPT][8], e[VPT][8];
+    bf16x8 ca[VPT], cb[VPT], ce[VPT];
     const float r = nr;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      unpack8(na[v], a[v]);
-      unpack8(nb[v], b[v]);
-      if (dres) unpack8(ne[v], e[v]);
+      ca[v] = na[v];
+      cb[v] = nb[v];
+      if (dres) ce[v] = ne[v];
     }
     if (row + gridDim.x < T) fetch(row + gridDim.x);
     float dot = 0.f;
 #pragma unroll
-    for (int v = 0; v < VPT; ++v)
+    for (int v = 0; v < VPT; ++v) {
+      float a[8], b[8], g[8];
+      unpack8(ca[v], a);
+      unpack8(cb[v], b);
+      unpack8(gw[v], g);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        b[v][j] *= r;                       // xhat
-        dot += a[v][j] * g[v][j] * b[v][j];
-      }
+      for (int j = 0; j < 8; ++j) dot += a[j] * g[j] * (b[j] * r);
+    }
     dot = block_sum_once(dot, scratch, parity) / D;
     bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * D);
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
-      float o[8];
+      float a[8], b[8], g[8], o[8];
+      unpack8(ca[v], a);
+      unpack8(cb[v], b);
+      unpack8(gw[v], g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        o[j] = r * (a[v][j] * g[v][j] - b[v][j] * dot);
-        dw[v][j] += a[v][j] * b[v][j];
-        if (dres) o[j] += e[v][j];
+        const float xhat = b[j] * r;
+        o[j] = r * (a[j] * g[j] - xhat * dot);
+        dw[v][j] += a[j] * xhat;
+      }
+      if (dres) {
+        float e[8];
+        unpack8(ce[v], e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += e[j];
       }
       dxr[threadIdx.x + v * NORM_THREADS] = pack8(o);
     }
@@ -321,10 +335,10 @@ rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16
 }
 
 // dw[c] (+)= sum_b partial[b][c]; fp32 output (the flat gradient bucket) or
-// bf16 when dw_bf16 is given.  A block owns 32 columns; its 8 thread rows each
+// bf16 when dw_bf16 is given.  A block owns 32 columns; its 32 thread rows each
 // sum a contiguous slice of the partials and the slices are added in a fixed
 // order, so the result does not depend on timing.
-constexpr int RED_SLICES = 8;
+constexpr int RED_SLICES = 32;
 __global__ void __launch_bounds__(32 * RED_SLICES)
 reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int D,
                        float* __restrict__ dw_f32, __nv_bfloat16* __restrict__ dw_bf16,
@@ -335,8 +349,10 @@ reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int D,
   const int b0 = threadIdx.y * per;
   const int b1 = min(nblocks, b0 + per);
   float s = 0.f;
-  if (c < D)
+  if (c < D) {
+#pragma unroll 4
     for (int b = b0; b < b1; ++b) s += partial[static_cast<long long>(b) * D + c];
+  }
   part[threadIdx.y][threadIdx.x] = s;
   __syncthreads();
   if (threadIdx.y != 0 || c >= D) return;

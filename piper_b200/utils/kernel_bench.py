@@ -105,6 +105,19 @@ def main(argv=None):
     w = torch.randn(4096, device=dev, dtype=torch.bfloat16)
     ms = _time(lambda: ops.rmsnorm(x, w), flush=flush)
     rows.append({"kernel": "rmsnorm_fwd:4096x4096", "ms": ms, "gbs": 2 * x.numel() * 2 / ms / 1e6})
+    res = torch.randn_like(x)
+    ms_add = _time(lambda: ops.add_rmsnorm(x, res, w, 1e-6), flush=flush)
+    rows.append({"kernel": "add_rmsnorm_fwd:4096x4096", "ms": ms_add, "gbs": 4 * x.numel() * 2 / ms_add / 1e6})
+    xg, wg = x.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    gy = torch.randn_like(x)
+
+    def norm_fb():
+        xg.grad = None
+        wg.grad = None
+        ops.rmsnorm(xg, wg).backward(gy)
+    ms_fb = _time(norm_fb, flush=flush)
+    rows.append({"kernel": "rmsnorm_fwd+bwd:4096x4096", "ms": ms_fb, "bwd_ms": ms_fb - ms,
+                 "bwd_gbs": 3 * x.numel() * 2 / max(ms_fb - ms, 1e-6) / 1e6})
     h13 = torch.randn(T, 28672, device=dev, dtype=torch.bfloat16)
     ms = _time(lambda: ops.swiglu(h13), flush=flush)
     rows.append({"kernel": "swiglu_fwd:4096x14336", "ms": ms, "gbs": 3 * T * 14336 * 2 / ms / 1e6})

@@ -87,11 +87,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             list(pool.map(lambda c: _run(c, verbose), jobs))
     need_link = force or bool(jobs) or not LIB.exists()
     if need_link:
-        cmd = ["g++", "-shared", "-o", str(LIB), *map(str, objects)]
+        tmp = LIB.with_name(LIB.name + f".{os.getpid()}.tmp")   # link aside, then rename: readers never see a partial file
+        cmd = ["g++", "-shared", "-o", str(tmp), *map(str, objects)]
         for d in libdirs:
             cmd += [f"-L{d}", f"-Wl,-rpath,{d}"]
         cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"]
-        _run(cmd, verbose)
+        try:
+            _run(cmd, verbose)
+            os.replace(tmp, LIB)
+        finally:
+            if tmp.exists():
+                tmp.unlink()
     return LIB
 
 

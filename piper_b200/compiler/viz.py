@@ -38,8 +38,8 @@ def _render(dot_source: str, output_path: str) -> str:
         try:
             subprocess.run([exe, "-Tpng", src, "-o", output_path + ".png"], check=True, timeout=120)
             return output_path + ".png"
-        except Exception:
-            pass
+        except (subprocess.SubprocessError, OSError):
+            pass   # graphviz failed: the caller still gets the .dot source
     return src
 
 

@@ -364,134 +364,215 @@ reduce_partials_kernel(const float* __restrict__ partial, int nblocks, int D,
 }
 
 // --------------------------------------------------------- QK-norm + RoPE
-// qkv is the packed projection [T, (Hq + 2*Hkv) * hd].  One warp handles one
-// (token, head) vector of hd = 128 or 64 elements; v heads are copied.
+// qkv is the packed projection [T, (Hq + 2*Hkv) * hd], hd = 128 or 64; v heads are copied.
 // rope pairs: interleaved (x[2i], x[2i+1]) or half-split (x[i], x[i+hd/2]).
 // cos/sin are fp32 [S, hd/2]; position of token t is t % S.
+//
+// A group of hd/16 lanes handles one (token, head) vector.  Every lane owns two 16-byte vectors chosen so
+// that both members of each of its eight rope pairs are its own: elements [16l, 16l+16) in the interleaved
+// form, [8l, 8l+8) and [hd/2 + 8l, hd/2 + 8l + 8) in the half-split form.  In both forms the lane's pairs use
+// cos/sin entries [8l, 8l+8).
+// A lane group walks this many consecutive heads of one token, so the token's cos/sin entries are loaded once.
+constexpr int ROPE_HEADS_PER_GROUP = 8;
+
 template <int HD>
-__global__ void qk_rope_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                               const float* __restrict__ cosp, const float* __restrict__ sinp,
-                               const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
-                               float* __restrict__ rstd_out, long long T, int S, int Hq, int Hkv,
-                               int interleaved, float eps, float sin_sign) {
-  constexpr int PER = HD / 32;   // elements per lane (4 or 2)
+struct RopeGroup {
+  static constexpr int LANES = HD / 16;
+  int lane, off0, off1;
+  unsigned mask;
+  __device__ __forceinline__ RopeGroup(int interleaved) {
+    const int wl = threadIdx.x & 31;
+    lane = wl & (LANES - 1);
+    mask = ((LANES == 32 ? 0u : (1u << LANES)) - 1u) << (wl & ~(LANES - 1));
+    off0 = interleaved ? 16 * lane : 8 * lane;
+    off1 = interleaved ? 16 * lane + 8 : HD / 2 + 8 * lane;
+  }
+  __device__ __forceinline__ float sum(float v) const {
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
+    return v;
+  }
+};
+
+// (a, b) -> (a*c - b*s, a*s + b*c) on the lane's eight pairs.
+__device__ __forceinline__ void rope_rotate(float (&v0)[8], float (&v1)[8], const float (&c)[8], const float (&s)[8],
+                                            int interleaved) {
+  if (interleaved) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float a0 = v0[2 * p], b0 = v0[2 * p + 1], a1 = v1[2 * p], b1 = v1[2 * p + 1];
+      v0[2 * p] = a0 * c[p] - b0 * s[p];
+      v0[2 * p + 1] = a0 * s[p] + b0 * c[p];
+      v1[2 * p] = a1 * c[4 + p] - b1 * s[4 + p];
+      v1[2 * p + 1] = a1 * s[4 + p] + b1 * c[4 + p];
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = v0[j], b = v1[j];
+      v0[j] = a * c[j] - b * s[j];
+      v1[j] = a * s[j] + b * c[j];
+    }
+  }
+}
+
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8], float scale) {
+  const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = lo.x * scale; f[1] = lo.y * scale; f[2] = lo.z * scale; f[3] = lo.w * scale;
+  f[4] = hi.x * scale; f[5] = hi.y * scale; f[6] = hi.z * scale; f[7] = hi.w * scale;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256)
+qk_rope_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+               const float* __restrict__ cosp, const float* __restrict__ sinp,
+               const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+               float* __restrict__ rstd_out, long long T, int S, int Hq, int Hkv,
+               int interleaved, float eps, float sin_sign) {
+  const RopeGroup<HD> g(interleaved);
+  constexpr int LANES = RopeGroup<HD>::LANES;
   const int heads = Hq + 2 * Hkv;
-  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (gw >= T * heads) return;
-  const long long t = gw / heads;
-  const int h = static_cast<int>(gw % heads);
-  const __nv_bfloat16* src = in + gw * HD;
-  __nv_bfloat16* dst = out + gw * HD;
-  // Lane owns PER consecutive elements in the interleaved form, or elements
-  // {j, j+HD/2} pairs in the half-split form.
-  float v[PER];
-  int idx[PER];
+  const int chunks = (heads + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP;
+  const long long total = T * chunks;
+  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x / LANES);
+  for (long long gi = static_cast<long long>(blockIdx.x) * (blockDim.x / LANES) + threadIdx.x / LANES; gi < total;
+       gi += stride) {
+    const long long t = gi / chunks;
+    const int h0 = static_cast<int>(gi - t * chunks) * ROPE_HEADS_PER_GROUP;
+    const int h1 = min(heads, h0 + ROPE_HEADS_PER_GROUP);
+    float c[8], s[8];
+    const long long cs = static_cast<long long>(t % S) * (HD / 2) + 8 * g.lane;
+    load8f(cosp + cs, c, 1.f);
+    load8f(sinp + cs, s, sin_sign);
+#pragma unroll 4
+    for (int h = h0; h < h1; ++h) {
+      const __nv_bfloat16* src = in + (t * heads + h) * HD;
+      __nv_bfloat16* dst = out + (t * heads + h) * HD;
+      const bf16x8 p0 = *reinterpret_cast<const bf16x8*>(src + g.off0);
+      const bf16x8 p1 = *reinterpret_cast<const bf16x8*>(src + g.off1);
+      if (h >= Hq + Hkv) {   // value head: plain copy
+        *reinterpret_cast<bf16x8*>(dst + g.off0) = p0;
+        *reinterpret_cast<bf16x8*>(dst + g.off1) = p1;
+        continue;
+      }
+      float v0[8], v1[8];
+      unpack8(p0, v0);
+      unpack8(p1, v1);
+      const __nv_bfloat16* nw = (h < Hq) ? qw : kw;
+      if (nw != nullptr) {
+        float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    if (interleaved) idx[j] = lane * PER + j;
-    else idx[j] = (j & 1) * (HD / 2) + lane * (PER / 2) + (j >> 1);
-    v[j] = __bfloat162float(src[idx[j]]);
-  }
-  if (h >= Hq + Hkv) {   // value head: plain copy
+        for (int j = 0; j < 8; ++j) ss += v0[j] * v0[j] + v1[j] * v1[j];
+        ss = g.sum(ss);
+        const float r = rsqrtf(ss / HD + eps);
+        if (rstd_out != nullptr && g.lane == 0) rstd_out[t * (Hq + Hkv) + h] = r;
+        float w0[8], w1[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(nw + g.off0), w0);
+        unpack8(*reinterpret_cast<const bf16x8*>(nw + g.off1), w1);
 #pragma unroll
-    for (int j = 0; j < PER; ++j) dst[idx[j]] = __float2bfloat16(v[j]);
-    return;
-  }
-  const __nv_bfloat16* nw = (h < Hq) ? qw : kw;
-  if (nw != nullptr) {
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) ss += v[j] * v[j];
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / HD + eps);
-    if (rstd_out != nullptr && lane == 0) rstd_out[t * (Hq + Hkv) + h] = r;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) v[j] = v[j] * r * __bfloat162float(nw[idx[j]]);
-  }
-  const int pos = static_cast<int>(t % S);
-#pragma unroll
-  for (int j = 0; j < PER; j += 2) {
-    const int pair = interleaved ? (idx[j] >> 1) : idx[j];   // index into [0, HD/2)
-    const float c = cosp[static_cast<long long>(pos) * (HD / 2) + pair];
-    const float s = sin_sign * sinp[static_cast<long long>(pos) * (HD / 2) + pair];
-    const float a = v[j], b = v[j + 1];
-    dst[idx[j]] = __float2bfloat16(a * c - b * s);
-    dst[idx[j + 1]] = __float2bfloat16(a * s + b * c);
+        for (int j = 0; j < 8; ++j) {
+          v0[j] = v0[j] * r * w0[j];
+          v1[j] = v1[j] * r * w1[j];
+        }
+      }
+      rope_rotate(v0, v1, c, s, interleaved);
+      *reinterpret_cast<bf16x8*>(dst + g.off0) = pack8(v0);
+      *reinterpret_cast<bf16x8*>(dst + g.off1) = pack8(v1);
+    }
   }
 }
 
 // Backward of QK-norm + RoPE: un-rotate the incoming gradient (RoPE is an
 // orthogonal map, so its transpose is the rotation by -theta), then apply the
-// RMSNorm backward per head; weight-gradient contributions are atomically
-// added to fp32 dqw/dkw (hd values each, negligible traffic).
+// RMSNorm backward per head.  Weight-gradient contributions are summed in
+// shared memory per CTA and added to fp32 dqw/dkw with one atomic per element
+// and CTA.
 template <int HD>
-__global__ void qk_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
-                                   const __nv_bfloat16* __restrict__ in /*pre-norm qkv*/,
-                                   __nv_bfloat16* __restrict__ din, const float* __restrict__ cosp,
-                                   const float* __restrict__ sinp, const __nv_bfloat16* __restrict__ qw,
-                                   const __nv_bfloat16* __restrict__ kw, float* __restrict__ dqw,
-                                   float* __restrict__ dkw, long long T, int S, int Hq, int Hkv,
-                                   int interleaved, float eps) {
-  constexpr int PER = HD / 32;
+__global__ void __launch_bounds__(256)
+qk_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ in /*pre-norm qkv*/,
+                   __nv_bfloat16* __restrict__ din, const float* __restrict__ cosp,
+                   const float* __restrict__ sinp, const __nv_bfloat16* __restrict__ qw,
+                   const __nv_bfloat16* __restrict__ kw, float* __restrict__ dqw,
+                   float* __restrict__ dkw, long long T, int S, int Hq, int Hkv,
+                   int interleaved, float eps) {
+  __shared__ float sdw[2][HD];
+  const bool want_dw = dqw != nullptr || dkw != nullptr;
+  if (want_dw) {
+    for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
+    __syncthreads();
+  }
+  const RopeGroup<HD> g(interleaved);
+  constexpr int LANES = RopeGroup<HD>::LANES;
   const int heads = Hq + 2 * Hkv;
-  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (gw >= T * heads) return;
-  const long long t = gw / heads;
-  const int h = static_cast<int>(gw % heads);
-  const __nv_bfloat16* g = dout + gw * HD;
-  __nv_bfloat16* dst = din + gw * HD;
-  float d[PER];
-  int idx[PER];
+  const int chunks = (heads + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP;
+  const long long total = T * chunks;
+  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x / LANES);
+  for (long long gi = static_cast<long long>(blockIdx.x) * (blockDim.x / LANES) + threadIdx.x / LANES; gi < total;
+       gi += stride) {
+    const long long t = gi / chunks;
+    const int h0 = static_cast<int>(gi - t * chunks) * ROPE_HEADS_PER_GROUP;
+    const int h1 = min(heads, h0 + ROPE_HEADS_PER_GROUP);
+    float c[8], s[8];
+    const long long cs = static_cast<long long>(t % S) * (HD / 2) + 8 * g.lane;
+    load8f(cosp + cs, c, 1.f);
+    load8f(sinp + cs, s, -1.f);
+#pragma unroll 4
+    for (int h = h0; h < h1; ++h) {
+      const __nv_bfloat16* gp = dout + (t * heads + h) * HD;
+      __nv_bfloat16* dst = din + (t * heads + h) * HD;
+      const bf16x8 p0 = *reinterpret_cast<const bf16x8*>(gp + g.off0);
+      const bf16x8 p1 = *reinterpret_cast<const bf16x8*>(gp + g.off1);
+      if (h >= Hq + Hkv) {
+        *reinterpret_cast<bf16x8*>(dst + g.off0) = p0;
+        *reinterpret_cast<bf16x8*>(dst + g.off1) = p1;
+        continue;
+      }
+      float d0[8], d1[8];
+      unpack8(p0, d0);
+      unpack8(p1, d1);
+      rope_rotate(d0, d1, c, s, interleaved);
+      const __nv_bfloat16* nw = (h < Hq) ? qw : kw;
+      if (nw != nullptr) {
+        const __nv_bfloat16* src = in + (t * heads + h) * HD;
+        float x0[8], x1[8], w0[8], w1[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(src + g.off0), x0);
+        unpack8(*reinterpret_cast<const bf16x8*>(src + g.off1), x1);
+        unpack8(*reinterpret_cast<const bf16x8*>(nw + g.off0), w0);
+        unpack8(*reinterpret_cast<const bf16x8*>(nw + g.off1), w1);
+        float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    if (interleaved) idx[j] = lane * PER + j;
-    else idx[j] = (j & 1) * (HD / 2) + lane * (PER / 2) + (j >> 1);
-    d[j] = __bfloat162float(g[idx[j]]);
-  }
-  if (h >= Hq + Hkv) {
+        for (int j = 0; j < 8; ++j) ss += x0[j] * x0[j] + x1[j] * x1[j];
+        ss = g.sum(ss);
+        const float r = rsqrtf(ss / HD + eps);
+        float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) dst[idx[j]] = __float2bfloat16(d[j]);
-    return;
-  }
-  const int pos = static_cast<int>(t % S);
+        for (int j = 0; j < 8; ++j) dot += (d0[j] * w0[j] * x0[j] + d1[j] * w1[j] * x1[j]) * r;
+        dot = g.sum(dot) / HD;
+        float* acc = sdw[h < Hq ? 0 : 1];
+        const bool add = (h < Hq ? dqw : dkw) != nullptr;
 #pragma unroll
-  for (int j = 0; j < PER; j += 2) {
-    const int pair = interleaved ? (idx[j] >> 1) : idx[j];
-    const float c = cosp[static_cast<long long>(pos) * (HD / 2) + pair];
-    const float s = sinp[static_cast<long long>(pos) * (HD / 2) + pair];
-    const float a = d[j], b = d[j + 1];
-    d[j] = a * c + b * s;
-    d[j + 1] = -a * s + b * c;
-  }
-  const __nv_bfloat16* nw = (h < Hq) ? qw : kw;
-  if (nw != nullptr) {
-    const __nv_bfloat16* src = in + gw * HD;
-    float x[PER], wv[PER];
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      x[j] = __bfloat162float(src[idx[j]]);
-      wv[j] = __bfloat162float(nw[idx[j]]);
-      ss += x[j] * x[j];
+        for (int j = 0; j < 8; ++j) {
+          const float xh0 = x0[j] * r, xh1 = x1[j] * r;
+          if (add) {
+            atomicAdd(acc + g.off0 + j, d0[j] * xh0);
+            atomicAdd(acc + g.off1 + j, d1[j] * xh1);
+          }
+          d0[j] = r * (d0[j] * w0[j] - xh0 * dot);
+          d1[j] = r * (d1[j] * w1[j] - xh1 * dot);
+        }
+      }
+      *reinterpret_cast<bf16x8*>(dst + g.off0) = pack8(d0);
+      *reinterpret_cast<bf16x8*>(dst + g.off1) = pack8(d1);
     }
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / HD + eps);
-    float dot = 0.f;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) dot += d[j] * wv[j] * x[j] * r;
-    dot = warp_sum(dot) / HD;
-    float* dwp = (h < Hq) ? dqw : dkw;
-#pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const float xhat = x[j] * r;
-      if (dwp != nullptr) atomicAdd(dwp + idx[j], d[j] * xhat);
-      d[j] = r * (d[j] * wv[j] - xhat * dot);
+  }
+  if (want_dw) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * HD; i += blockDim.x) {
+      float* dwp = i < HD ? dqw : dkw;
+      const float v = (&sdw[0][0])[i];
+      if (dwp != nullptr && v != 0.f) atomicAdd(dwp + (i < HD ? i : i - HD), v);
     }
   }
-#pragma unroll
-  for (int j = 0; j < PER; ++j) dst[idx[j]] = __float2bfloat16(d[j]);
 }
 
 // ------------------------------------------------------------------- SwiGLU
@@ -693,6 +774,12 @@ __global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_
   }
 }
 
+// True when every non-null pointer is 16-byte aligned (the kernels use 16-byte vector accesses).
+template <typename... P>
+inline bool aligned16(P... ptrs) {
+  return ((reinterpret_cast<uintptr_t>(static_cast<const void*>(ptrs)) | ...) & 15u) == 0;
+}
+
 inline int grid_for(long long work, int threads, int max_blocks = 148 * 16) {
   long long b = (work + threads - 1) / threads;
   if (b > max_blocks) b = max_blocks;
@@ -770,10 +857,12 @@ int rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
 int qk_rope_fwd(const void* in, void* out, const float* cosp, const float* sinp, const void* qw,
                 const void* kw, long long T, int S, int Hq, int Hkv, int hd, int interleaved, float eps,
                 cudaStream_t st) {
-  const long long warps = T * (Hq + 2 * Hkv);
-  if (warps == 0) return 0;
+  const long long groups = T * ((Hq + 2 * Hkv + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP);
+  if (groups == 0) return 0;
+  if (hd != 128 && hd != 64) return -1;
+  if (!aligned16(in, out, cosp, sinp, qw, kw)) return -4;
   const int threads = 256;
-  const unsigned blocks = static_cast<unsigned>((warps * 32 + threads - 1) / threads);
+  const int blocks = grid_for(groups * (hd / 16), threads);
   auto a = static_cast<const __nv_bfloat16*>(in);
   auto o = static_cast<__nv_bfloat16*>(out);
   auto q = static_cast<const __nv_bfloat16*>(qw);
@@ -792,10 +881,12 @@ int qk_rope_fwd(const void* in, void* out, const float* cosp, const float* sinp,
 int qk_rope_bwd(const void* dout, const void* in, void* din, const float* cosp, const float* sinp,
                 const void* qw, const void* kw, float* dqw, float* dkw, long long T, int S, int Hq,
                 int Hkv, int hd, int interleaved, float eps, cudaStream_t st) {
-  const long long warps = T * (Hq + 2 * Hkv);
-  if (warps == 0) return 0;
+  const long long groups = T * ((Hq + 2 * Hkv + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP);
+  if (groups == 0) return 0;
+  if (hd != 128 && hd != 64) return -1;
+  if (!aligned16(dout, in, din, cosp, sinp, qw, kw)) return -4;
   const int threads = 256;
-  const unsigned blocks = static_cast<unsigned>((warps * 32 + threads - 1) / threads);
+  const int blocks = grid_for(groups * (hd / 16), threads);
   auto g = static_cast<const __nv_bfloat16*>(dout);
   auto a = static_cast<const __nv_bfloat16*>(in);
   auto o = static_cast<__nv_bfloat16*>(din);

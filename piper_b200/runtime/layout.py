@@ -124,8 +124,8 @@ class ProcessGroups:
                 try:
                     opts.config.max_ctas = int(os.environ.get("PIPER_P2P_MAX_CTAS", "8"))
                     opts.config.min_ctas = 1
-                except Exception:
-                    pass
+                except (AttributeError, TypeError, ValueError):
+                    pass   # a torch build whose NCCL options lack these fields: run with NCCL's defaults
                 pg = dist.new_group(ranks=sorted((a, b)), backend=self.backend, timeout=self.timeout, pg_options=opts)
                 if self.layout.global_rank in (a, b):
                     self._channels[ch] = pg

@@ -118,6 +118,10 @@ def main(argv=None):
     ms_fb = _time(norm_fb, flush=flush)
     rows.append({"kernel": "rmsnorm_fwd+bwd:4096x4096", "ms": ms_fb, "bwd_ms": ms_fb - ms,
                  "bwd_gbs": 3 * x.numel() * 2 / max(ms_fb - ms, 1e-6) / 1e6})
+    cos, sin = ops.rope_tables(128, T, 500000.0, device=dev)
+    qkv = torch.randn(T, 48 * 128, device=dev, dtype=torch.bfloat16)
+    ms = _time(lambda: ops.qk_rope(qkv, cos, sin, None, None, T, 32, 8, 128, True, 1e-6), flush=flush)
+    rows.append({"kernel": "qk_rope_fwd:4096x(32+2*8)x128", "ms": ms, "gbs": 2 * qkv.numel() * 2 / ms / 1e6})
     h13 = torch.randn(T, 28672, device=dev, dtype=torch.bfloat16)
     ms = _time(lambda: ops.swiglu(h13), flush=flush)
     rows.append({"kernel": "swiglu_fwd:4096x14336", "ms": ms, "gbs": 3 * T * 14336 * 2 / ms / 1e6})

@@ -130,15 +130,18 @@ def test_rmsnorm_and_residual(T, D):
     assert _rel_err(y2, x0 * torch.rsqrt(x0.pow(2).mean(-1, keepdim=True) + 1e-6) * w.detach().float()) < 1e-2
 
 
-@pytest.mark.parametrize("hd,inter,qknorm", [(128, True, False), (128, False, True), (64, False, False), (64, True, True)])
-def test_qk_rope(hd, inter, qknorm):
+@pytest.mark.parametrize("hd,inter,qknorm,seqs", [(128, True, False, 2), (128, False, True, 2), (64, False, False, 2),
+                                                  (64, True, True, 2), (128, False, True, 640), (64, True, True, 1200)])
+def test_qk_rope(hd, inter, qknorm, seqs):
+    """The large cases use 12 heads (two head chunks per token, the second one partial) and more tokens than one
+    pass of the grid covers."""
     from piper_b200 import ops
     from piper_b200.ops.core import _qk_rope_ref
 
     torch.manual_seed(4)
-    S, Hq, Hkv = 64, 4, 2
+    S, Hq, Hkv = (64, 4, 2) if seqs == 2 else (64, 8, 2)
     cos, sin = ops.rope_tables(hd, S, 10000.0, device="cuda")
-    qkv = torch.randn(2 * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    qkv = torch.randn(seqs * S, (Hq + 2 * Hkv) * hd, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     qw = torch.randn(hd, device="cuda", dtype=torch.bfloat16, requires_grad=True) if qknorm else None
     kw = torch.randn(hd, device="cuda", dtype=torch.bfloat16, requires_grad=True) if qknorm else None
     out = ops.qk_rope(qkv, cos, sin, qw, kw, S, Hq, Hkv, hd, inter, 1e-6)

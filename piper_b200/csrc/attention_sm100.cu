@@ -439,12 +439,11 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
   const int wl = threadIdx.x & 31;
   const int lane = wl & (LANES - 1);
   const unsigned mask = ((1u << LANES) - 1u) << (wl & ~(LANES - 1));
-  const long long total = T * Hq;
-  const long long stride = static_cast<long long>(gridDim.x) * (256 / LANES);
-  for (long long gi = static_cast<long long>(blockIdx.x) * (256 / LANES) + threadIdx.x / LANES; gi < total;
-       gi += stride) {
-    const uint4 a = *reinterpret_cast<const uint4*>(o + gi * HD + 8 * lane);
-    const uint4 b = *reinterpret_cast<const uint4*>(d_o + gi * HD + 8 * lane);
+  const unsigned total = static_cast<unsigned>(T * Hq);   // the launcher keeps T * Hq below 2^31
+  const unsigned stride = gridDim.x * (256 / LANES);
+  for (unsigned gi = blockIdx.x * (256 / LANES) + threadIdx.x / LANES; gi < total; gi += stride) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + static_cast<long long>(gi) * HD + 8 * lane);
+    const uint4 b = *reinterpret_cast<const uint4*>(d_o + static_cast<long long>(gi) * HD + 8 * lane);
     const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&a);
     const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&b);
     float s = 0.f;
@@ -455,9 +454,9 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __re
     }
 #pragma unroll
     for (int off = LANES / 2; off > 0; off >>= 1) s += __shfl_xor_sync(mask, s, off);
-    const long long t = gi / Hq;
-    const int h = static_cast<int>(gi - t * Hq);
-    if (lane == 0) delta[((t / S) * Hq + h) * S + (t % S)] = s;
+    const unsigned t = gi / static_cast<unsigned>(Hq), h = gi - t * Hq;
+    const unsigned bi = t / static_cast<unsigned>(S), si = t - bi * S;
+    if (lane == 0) delta[(static_cast<long long>(bi) * Hq + h) * S + si] = s;
   }
 }
 
@@ -909,6 +908,7 @@ static int attn_bwd_impl(const void* qkv, const void* out, const void* d_out, co
     cfg = true;
   }
   if (((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(d_out)) & 15u) != 0) return -1;
+  if (T * Hq >= (1ll << 31)) return -1;
   const long long delta_blocks = (T * Hq * (HD / 8) + 255) / 256;
   attn_delta_kernel<HD><<<static_cast<unsigned>(delta_blocks < 148 * 16 ? delta_blocks : 148 * 16), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out), delta, T, S, Hq);

@@ -433,15 +433,14 @@ qk_rope_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
   constexpr int LANES = RopeGroup<HD>::LANES;
   const int heads = Hq + 2 * Hkv;
   const int chunks = (heads + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP;
-  const long long total = T * chunks;
-  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x / LANES);
-  for (long long gi = static_cast<long long>(blockIdx.x) * (blockDim.x / LANES) + threadIdx.x / LANES; gi < total;
-       gi += stride) {
-    const long long t = gi / chunks;
-    const int h0 = static_cast<int>(gi - t * chunks) * ROPE_HEADS_PER_GROUP;
+  const unsigned total = static_cast<unsigned>(T) * chunks;   // the launcher keeps this below 2^31
+  const unsigned stride = gridDim.x * (blockDim.x / LANES);
+  for (unsigned gi = blockIdx.x * (blockDim.x / LANES) + threadIdx.x / LANES; gi < total; gi += stride) {
+    const long long t = gi / static_cast<unsigned>(chunks);
+    const int h0 = static_cast<int>(gi - static_cast<unsigned>(t) * chunks) * ROPE_HEADS_PER_GROUP;
     const int h1 = min(heads, h0 + ROPE_HEADS_PER_GROUP);
     float c[8], s[8];
-    const long long cs = static_cast<long long>(t % S) * (HD / 2) + 8 * g.lane;
+    const int cs = static_cast<int>(static_cast<unsigned>(t) % static_cast<unsigned>(S)) * (HD / 2) + 8 * g.lane;
     load8f(cosp + cs, c, 1.f);
     load8f(sinp + cs, s, sin_sign);
 #pragma unroll 4
@@ -505,15 +504,14 @@ qk_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* 
   constexpr int LANES = RopeGroup<HD>::LANES;
   const int heads = Hq + 2 * Hkv;
   const int chunks = (heads + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP;
-  const long long total = T * chunks;
-  const long long stride = static_cast<long long>(gridDim.x) * (blockDim.x / LANES);
-  for (long long gi = static_cast<long long>(blockIdx.x) * (blockDim.x / LANES) + threadIdx.x / LANES; gi < total;
-       gi += stride) {
-    const long long t = gi / chunks;
-    const int h0 = static_cast<int>(gi - t * chunks) * ROPE_HEADS_PER_GROUP;
+  const unsigned total = static_cast<unsigned>(T) * chunks;   // the launcher keeps this below 2^31
+  const unsigned stride = gridDim.x * (blockDim.x / LANES);
+  for (unsigned gi = blockIdx.x * (blockDim.x / LANES) + threadIdx.x / LANES; gi < total; gi += stride) {
+    const long long t = gi / static_cast<unsigned>(chunks);
+    const int h0 = static_cast<int>(gi - static_cast<unsigned>(t) * chunks) * ROPE_HEADS_PER_GROUP;
     const int h1 = min(heads, h0 + ROPE_HEADS_PER_GROUP);
     float c[8], s[8];
-    const long long cs = static_cast<long long>(t % S) * (HD / 2) + 8 * g.lane;
+    const int cs = static_cast<int>(static_cast<unsigned>(t) % static_cast<unsigned>(S)) * (HD / 2) + 8 * g.lane;
     load8f(cosp + cs, c, 1.f);
     load8f(sinp + cs, s, -1.f);
 #pragma unroll 4
@@ -577,35 +575,51 @@ qk_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* 
 
 // ------------------------------------------------------------------- SwiGLU
 // h13 = [gate | up] of width 2F per row; act = silu(gate) * up.
-__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ act,
-                                  long long T, int F) {
-  const long long nvec = T * (F / 8);
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = i / (F / 8);
-    const int c = static_cast<int>(i % (F / 8));
-    const bf16x8* base = reinterpret_cast<const bf16x8*>(h13 + row * 2 * F);
+// Threads walk the flattened [T][F/8] vector index with a grid stride; row and column advance incrementally
+// (stride_rows, stride_cols = stride / (F/8), stride % (F/8) come from the host), so the loop has no division.
+struct VecWalk {
+  long long row;
+  int c;
+  __device__ __forceinline__ VecWalk(int vecs) {
+    const long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    row = i0 / vecs;
+    c = static_cast<int>(i0 - row * vecs);
+  }
+  __device__ __forceinline__ void next(int vecs, int stride_rows, int stride_cols) {
+    row += stride_rows;
+    c += stride_cols;
+    if (c >= vecs) {
+      c -= vecs;
+      ++row;
+    }
+  }
+};
+
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ h13, __nv_bfloat16* __restrict__ act, long long T, int F,
+                  int stride_rows, int stride_cols) {
+  const int vecs = F / 8;
+  for (VecWalk w(vecs); w.row < T; w.next(vecs, stride_rows, stride_cols)) {
+    const bf16x8* base = reinterpret_cast<const bf16x8*>(h13 + w.row * 2 * F);
     float g[8], u[8], o[8];
-    unpack8(base[c], g);
-    unpack8(base[F / 8 + c], u);
+    unpack8(base[w.c], g);
+    unpack8(base[vecs + w.c], u);
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
-    reinterpret_cast<bf16x8*>(act + row * F)[c] = pack8(o);
+    reinterpret_cast<bf16x8*>(act + w.row * F)[w.c] = pack8(o);
   }
 }
 
-__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ h13, const __nv_bfloat16* __restrict__ dact,
-                                  __nv_bfloat16* __restrict__ dh13, long long T, int F) {
-  const long long nvec = T * (F / 8);
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long row = i / (F / 8);
-    const int c = static_cast<int>(i % (F / 8));
-    const bf16x8* base = reinterpret_cast<const bf16x8*>(h13 + row * 2 * F);
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ h13, const __nv_bfloat16* __restrict__ dact,
+                  __nv_bfloat16* __restrict__ dh13, long long T, int F, int stride_rows, int stride_cols) {
+  const int vecs = F / 8;
+  for (VecWalk w(vecs); w.row < T; w.next(vecs, stride_rows, stride_cols)) {
+    const bf16x8* base = reinterpret_cast<const bf16x8*>(h13 + w.row * 2 * F);
     float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(base[c], g);
-    unpack8(base[F / 8 + c], u);
-    unpack8(reinterpret_cast<const bf16x8*>(dact + row * F)[c], d);
+    unpack8(base[w.c], g);
+    unpack8(base[vecs + w.c], u);
+    unpack8(reinterpret_cast<const bf16x8*>(dact + w.row * F)[w.c], d);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float sg = 1.f / (1.f + __expf(-g[j]));
@@ -613,9 +627,9 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ h13, const _
       du[j] = d[j] * silu;
       dg[j] = d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
     }
-    bf16x8* ob = reinterpret_cast<bf16x8*>(dh13 + row * 2 * F);
-    ob[c] = pack8(dg);
-    ob[F / 8 + c] = pack8(du);
+    bf16x8* ob = reinterpret_cast<bf16x8*>(dh13 + w.row * 2 * F);
+    ob[w.c] = pack8(dg);
+    ob[vecs + w.c] = pack8(du);
   }
 }
 
@@ -860,6 +874,7 @@ int qk_rope_fwd(const void* in, void* out, const float* cosp, const float* sinp,
   const long long groups = T * ((Hq + 2 * Hkv + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP);
   if (groups == 0) return 0;
   if (hd != 128 && hd != 64) return -1;
+  if (groups >= (1ll << 31) || static_cast<long long>(S) * (hd / 2) >= (1ll << 31)) return -1;
   if (!aligned16(in, out, cosp, sinp, qw, kw)) return -4;
   const int threads = 256;
   const int blocks = grid_for(groups * (hd / 16), threads);
@@ -884,6 +899,7 @@ int qk_rope_bwd(const void* dout, const void* in, void* din, const float* cosp, 
   const long long groups = T * ((Hq + 2 * Hkv + ROPE_HEADS_PER_GROUP - 1) / ROPE_HEADS_PER_GROUP);
   if (groups == 0) return 0;
   if (hd != 128 && hd != 64) return -1;
+  if (groups >= (1ll << 31) || static_cast<long long>(S) * (hd / 2) >= (1ll << 31)) return -1;
   if (!aligned16(dout, in, din, cosp, sinp, qw, kw)) return -4;
   const int threads = 256;
   const int blocks = grid_for(groups * (hd / 16), threads);
@@ -906,17 +922,23 @@ int qk_rope_bwd(const void* dout, const void* in, void* din, const float* cosp, 
 int swiglu_fwd(const void* h13, void* act, long long T, int F, cudaStream_t st) {
   if (F % 8 != 0) return -1;
   if (T == 0) return 0;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(act), T, F);
+  const int vecs = F / 8;
+  const int blocks = grid_for(T * vecs, 256);
+  const long long stride = static_cast<long long>(blocks) * 256;
+  swiglu_fwd_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h13), static_cast<__nv_bfloat16*>(act), T,
+                                            F, static_cast<int>(stride / vecs), static_cast<int>(stride % vecs));
   return PIPER_LAUNCH_OK();
 }
 
 int swiglu_bwd(const void* h13, const void* dact, void* dh13, long long T, int F, cudaStream_t st) {
   if (F % 8 != 0) return -1;
   if (T == 0) return 0;
-  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(h13), static_cast<const __nv_bfloat16*>(dact),
-      static_cast<__nv_bfloat16*>(dh13), T, F);
+  const int vecs = F / 8;
+  const int blocks = grid_for(T * vecs, 256);
+  const long long stride = static_cast<long long>(blocks) * 256;
+  swiglu_bwd_kernel<<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(h13),
+                                            static_cast<const __nv_bfloat16*>(dact), static_cast<__nv_bfloat16*>(dh13),
+                                            T, F, static_cast<int>(stride / vecs), static_cast<int>(stride % vecs));
   return PIPER_LAUNCH_OK();
 }
 

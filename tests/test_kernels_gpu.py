@@ -179,6 +179,22 @@ def test_attention_fwd_bwd(B, S, Hq, Hkv, hd):
     assert _rel_err(gq[:, (Hq + Hkv) * hd:], gr[:, (Hq + Hkv) * hd:]) < 3e-2   # dV
 
 
+@pytest.mark.parametrize("T,F", [(9000, 776), (5000, 14336)])
+def test_swiglu_grid_stride_walk(T, F):
+    """More vectors than the grid has threads, with a row length that the grid stride does not divide."""
+    from piper_b200 import ops
+
+    torch.manual_seed(16)
+    h = torch.randn(T, 2 * F, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    a = ops.swiglu(h)
+    g = torch.randn_like(a)
+    a.backward(g)
+    hr = h.detach().float().requires_grad_(True)
+    ar = torch.nn.functional.silu(hr[:, :F]) * hr[:, F:]
+    ar.backward(g.float())
+    assert _rel_err(a, ar) < 1e-2 and _rel_err(h.grad, hr.grad) < 1e-2
+
+
 def test_swiglu_embedding_ce_adam():
     from piper_b200 import ops
     from piper_b200.ops import native

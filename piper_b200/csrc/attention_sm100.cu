@@ -30,6 +30,8 @@
 #include "attention_sm100.h"
 
 #include <cstdlib>
+#include <map>
+#include <mutex>
 
 #include "ptx.cuh"
 
@@ -888,6 +890,33 @@ int attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int Hq, int H
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// Side stream and the two events that fork the dK/dV kernel off a caller's stream and join it again; one set
+// per (device, caller stream), created on first use and kept for the life of the process.
+struct BwdFork {
+  cudaStream_t side = nullptr;
+  cudaEvent_t ready = nullptr, done = nullptr;
+};
+
+static bool bwd_fork(cudaStream_t st, BwdFork* out) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, BwdFork> forks;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = forks.find({dev, st});
+  if (it == forks.end()) {
+    BwdFork f;
+    int least = 0, greatest = 0;   // the long dK/dV CTAs should win SMs over the dQ CTAs queued behind them
+    if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return false;
+    if (cudaStreamCreateWithPriority(&f.side, cudaStreamNonBlocking, greatest) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&f.ready, cudaEventDisableTiming) != cudaSuccess) return false;
+    if (cudaEventCreateWithFlags(&f.done, cudaEventDisableTiming) != cudaSuccess) return false;
+    it = forks.emplace(std::make_pair(dev, st), f).first;
+  }
+  *out = it->second;
+  return true;
+}
+
 template <int HD>
 static int attn_bwd_impl(const void* qkv, const void* out, const void* d_out, const float* lse,
                          float* delta, void* d_qkv, int B, int S, int Hq, int Hkv, float softmax_scale,
@@ -913,13 +942,34 @@ static int attn_bwd_impl(const void* qkv, const void* out, const void* d_out, co
   attn_delta_kernel<HD><<<static_cast<unsigned>(delta_blocks < 148 * 16 ? delta_blocks : 148 * 16), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(d_out), delta, T, S, Hq);
   const float scale_log2 = softmax_scale * 1.4426950408889634f;
+  // The two gradient kernels are independent (dK/dV and dQ go to different columns of d_qkv) and each holds a
+  // whole SM per CTA.  The dK/dV grid is small (S/128 x Hkv CTAs, under two waves for eight KV heads), so its last
+  // wave leaves SMs idle.  With PIPER_ATTN_FORK=1 it is launched first on a high-priority side stream and the dQ
+  // CTAs fill those SMs; by default both kernels run one after the other on the caller's stream.
+  static int use_fork = -1;
+  if (use_fork < 0) {
+    const char* env = getenv("PIPER_ATTN_FORK");
+    use_fork = (env != nullptr && env[0] == '1') ? 1 : 0;
+  }
+  BwdFork fork;
+  cudaStream_t kv_stream = st;
+  if (use_fork) {
+    if (!bwd_fork(st, &fork)) return -3;
+    if (cudaEventRecord(fork.ready, st) != cudaSuccess || cudaStreamWaitEvent(fork.side, fork.ready, 0) != cudaSuccess)
+      return -3;
+    kv_stream = fork.side;
+  }
+  attn_bwd_kernel<HD, 1><<<dim3(S / 128, Hkv, B), BWD_THREADS, BwdSmem<HD>::TOTAL, kv_stream>>>(
+      tqx, tqy, tdx, tdy, lse, delta, static_cast<__nv_bfloat16*>(d_qkv), S, Hq, Hkv, softmax_scale,
+      scale_log2, status);
+  const bool kv_ok = cudaGetLastError() == cudaSuccess;
+  if (use_fork && cudaEventRecord(fork.done, fork.side) != cudaSuccess) return -3;
   attn_bwd_kernel<HD, 0><<<dim3(S / 128, Hq, B), BWD_THREADS, BwdSmem<HD>::TOTAL, st>>>(
       tqx, tqy, tdx, tdy, lse, delta, static_cast<__nv_bfloat16*>(d_qkv), S, Hq, Hkv, softmax_scale,
       scale_log2, status);
-  attn_bwd_kernel<HD, 1><<<dim3(S / 128, Hkv, B), BWD_THREADS, BwdSmem<HD>::TOTAL, st>>>(
-      tqx, tqy, tdx, tdy, lse, delta, static_cast<__nv_bfloat16*>(d_qkv), S, Hq, Hkv, softmax_scale,
-      scale_log2, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+  const bool q_ok = cudaGetLastError() == cudaSuccess;
+  if (use_fork && cudaStreamWaitEvent(st, fork.done, 0) != cudaSuccess) return -3;   // the caller's stream owns both
+  return kv_ok && q_ok ? 0 : -3;
 }
 
 int attn_set_trace(unsigned long long* buf) {

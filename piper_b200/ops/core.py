@@ -28,6 +28,7 @@ the weight-gradient GEMM writes where the gradient finally lives):
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -156,6 +157,43 @@ def _linear_wgrad(x2: Tensor, dy2: Tensor, w: Tensor) -> Optional[Tensor]:
     return dw.to(w.dtype)
 
 
+# The input-gradient and weight-gradient GEMMs of one linear layer are independent.  Each is a persistent kernel
+# with one CTA per SM whose last round of tiles leaves SMs idle (256 tiles on 148 SMs: 40 idle SMs in the second
+# round); launched on two streams, the CTAs of the second kernel start on the SMs the first one has left.
+# PIPER_GEMM_FORK=0 runs them one after the other on the current stream; 1 joins the side stream at the end of
+# every linear backward; 2 joins only when the enclosing ``deferred_join`` block ends (the executor wraps the
+# backward pass of a segment in one), so a weight-gradient GEMM may also run under the kernels that follow it.
+_GEMM_FORK = int(os.environ.get("PIPER_GEMM_FORK", "1") or 0)
+_side_streams: dict = {}
+
+
+class deferred_join:
+    """Scope inside which forked weight-gradient GEMMs are joined once, at exit, instead of per layer."""
+
+    depth = 0
+    pending: dict = {}
+
+    def __enter__(self):
+        deferred_join.depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        deferred_join.depth -= 1
+        if deferred_join.depth == 0:
+            for cur, side in deferred_join.pending.values():
+                cur.wait_stream(side)
+            deferred_join.pending.clear()
+        return False
+
+
+def _side_stream(cur: "torch.cuda.Stream") -> "torch.cuda.Stream":
+    key = (cur.device.index, cur.cuda_stream)
+    side = _side_streams.get(key)
+    if side is None:
+        side = _side_streams[key] = torch.cuda.Stream(device=cur.device)
+    return side
+
+
 def _linear_setup(ctx, inputs, output):
     x, w = inputs
     ctx.save_for_backward(x, w)
@@ -169,12 +207,32 @@ def _linear_backward(ctx, dy):
     x2 = x.reshape(-1, x.shape[-1])
     if not x2.is_contiguous():
         x2 = x2.contiguous()
+    deferred = wgrad_store.active is not None
+    if (_GEMM_FORK and ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and not deferred and _is_native(dy2)):
+        cur = torch.cuda.current_stream(dy2.device)
+        side = _side_stream(cur)
+        dw_out = None if grad_sinks.get(w) is not None else torch.empty_like(w)   # allocated on the current stream
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            if dw_out is None:
+                _linear_wgrad(x2, dy2, w)
+            else:
+                _gemm(dy2, x2, dw_out, True, True)
+        dx = _linear_dgrad(dy2, w).view(x.shape)
+        if _GEMM_FORK == 2 and deferred_join.depth > 0 and dw_out is None:
+            # the operands may be freed before the side stream has read them: tell the allocator
+            x2.record_stream(side)
+            dy2.record_stream(side)
+            deferred_join.pending[(cur.device.index, cur.cuda_stream)] = (cur, side)
+        else:
+            cur.wait_stream(side)   # everything later on this stream, frees of x and dy included, follows both GEMMs
+        return dx, dw_out
     dx = None
     if ctx.needs_input_grad[0]:
         dx = _linear_dgrad(dy2, w).view(x.shape)
     dw = None
     if ctx.needs_input_grad[1]:
-        if wgrad_store.active is not None:
+        if deferred:
             xd, dyd = x2.detach(), dy2.detach()
             wgrad_store.active.append((lambda: _linear_wgrad(xd, dyd, w), w))
         else:

@@ -573,6 +573,8 @@ class DagExecutor:
             outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
         if split:
             ops_core.wgrad_store.begin()
+        join_scope = ops_core.deferred_join()
+        join_scope.__enter__()
         try:
             if node.node_meta.get("compute_loss"):
                 labels = self._microbatch(a.labels, self._mb(node))
@@ -593,6 +595,7 @@ class DagExecutor:
                 if pairs:
                     torch.autograd.backward([p[0] for p in pairs], [p[1] for p in pairs])
         finally:
+            join_scope.__exit__(None, None, None)
             if split:
                 self.wgrad_queues[node.uid] = ops_core.wgrad_store.end()
         # one slot per input; a floating-point input that received no gradient reports zeros, so that both ends

@@ -20,7 +20,7 @@ from typing import Optional
 import torch
 from torch import Tensor
 
-from . import native
+from . import core, native
 from .core import _is_native, _require_bf16, grad_sinks, wgrad_store
 
 PAD = 128
@@ -235,6 +235,23 @@ def _glinear_backward(ctx, dy):
     rows, w, g_start, g_len = ctx.saved_tensors
     E, N, K = w.shape
     dyc = dy.contiguous()
+    if (core._GEMM_FORK and ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and wgrad_store.active is None
+            and _is_native(rows) and grad_sinks.get(w) is not None):
+        # same fork as in the dense linear backward: the weight-gradient GEMM runs on a side stream
+        cur = torch.cuda.current_stream(rows.device)
+        side = core._side_stream(cur)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            _grouped_wgrad(rows, dyc, w, g_start, g_len)
+        drows = torch.empty_like(rows, memory_format=torch.contiguous_format)
+        _grouped(1, None, dyc, w, drows, g_start, g_len, E, N, K)
+        if core._GEMM_FORK == 2 and core.deferred_join.depth > 0:
+            for t in (rows, dyc, g_start, g_len):
+                t.record_stream(side)
+            core.deferred_join.pending[(cur.device.index, cur.cuda_stream)] = (cur, side)
+        else:
+            cur.wait_stream(side)
+        return drows, None, None, None
     drows = None
     if ctx.needs_input_grad[0]:
         if _is_native(rows):

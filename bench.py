@@ -21,11 +21,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import statistics
-import subprocess
 import sys
-import threading
-import time
 
 PUBLISHED_TOKENS_PER_S = 13200.0   # "Piper eager, 1F1B" bar of the reference's figs/eval.png (hardware not stated)
 SEQ = 4096
@@ -52,55 +48,11 @@ def _schedule(n_gpus: int):
     return sched, pp, dp, mbs
 
 
-class _ClockSampler:
-    """Samples SM clock and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int) -> None:
-        self.index, self.rows, self.proc = index, [], None
-
-    def start(self) -> None:
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
-            threading.Thread(target=self._pump, daemon=True).start()
-        except Exception:
-            self.proc = None
-
-    def _pump(self) -> None:
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
-    def stop(self) -> dict:
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except Exception:
-                pass
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            if len(r) < 6:
-                continue
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, r[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
-
-
 def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
 
+    from baseline.clocks import ClockSampler
     from piper_b200 import piper_exec_dag, piper_setup
     from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer, balanced_stage_layers
     from piper_b200.nn import cross_entropy_loss
@@ -132,7 +84,7 @@ def run_ours(args) -> dict:
     native.check_status()
 
     def timed(step_fn):
-        sampler = _ClockSampler(local)
+        sampler = ClockSampler(local)
         sampler.start()
         barrier()
         k0 = native.lib().kernel_launch_count()
@@ -215,6 +167,12 @@ def main() -> int:
     out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps(out), flush=True)
+    if args.impl == "reference":
+        # the reference's actors own the process groups of this process (in other threads): leave without
+        # running their destructors, which would wait for peers that have already left
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     try:
         import torch.distributed as dist
         if dist.is_initialized():

@@ -828,6 +828,8 @@ int rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_
   return PIPER_LAUNCH_OK();
 }
 
+// Two strips per SM of a 148-SM part, whatever the device: the allocation-free entry point sizes its built-in
+// scratch array (PIPER_NOALLOC_MAX_STRIPS) from this fixed bound.
 int rmsnorm_bwd_num_partials(long long T) {
   const int cap = 148 * 2;
   return static_cast<int>(T < cap ? (T > 0 ? T : 1) : cap);
@@ -837,6 +839,7 @@ int rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
                 void* dx, float* dw_partial, float* dw_f32, void* dw_bf16, int accumulate, long long T,
                 int D, cudaStream_t st) {
   if (D % 8 != 0 || D * sizeof(float) > 160 * 1024) return -1;
+  if (T < 0 || T > 2147483647LL) return -1;      // the kernels index rows with a 32-bit int
   if (T == 0) return 0;
   const int nb = rmsnorm_bwd_num_partials(T);
   const dim3 red_grid((D + 31) / 32), red_block(32, RED_SLICES);

@@ -50,6 +50,7 @@ extern "C" int piper_rmsnorm_bwd_noalloc(const void* dy, const void* x, const vo
                                          cudaStream_t stream) {
   g_error[0] = '\0';
   if (T < 0) return fail(-1, "T must be non-negative, got %lld", T);
+  if (T > 2147483647LL) return fail(-1, "T = %lld exceeds the 32-bit row index of the kernels (max %lld)", T, 2147483647LL);
   if (D <= 0 || D % 8 != 0) return fail(-1, "D must be a positive multiple of 8, got %lld", D);
   if (D > PIPER_NOALLOC_MAX_D)
     return fail(-1, "D = %lld exceeds the built-in scratch size (PIPER_NOALLOC_MAX_D = %lld)", D,

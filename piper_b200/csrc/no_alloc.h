@@ -3,9 +3,9 @@
 // This entry point has no counterpart in the reference; it exists for
 // embedders of this library that run where cudaMalloc (and therefore every
 // allocating library routine, PyTorch's caching allocator included) is off
-// limits: code running inside a CUDA-graph capture, hosts that hand a plugin
-// a fixed memory budget up front, and real-time loops that must not take the
-// allocator's locks.  The normal entry point (piper::rmsnorm_bwd) needs a
+// limits: hosts that hand a plugin a fixed memory budget up front and forbid
+// later allocations, and real-time loops that must not take the allocator's
+// locks or risk its implicit device synchronisation.  The normal entry point (piper::rmsnorm_bwd) needs a
 // caller-provided scratch buffer for its per-strip partial sums of the weight
 // gradient; here that scratch is a fixed array inside the library image.
 #pragma once
@@ -18,7 +18,9 @@ extern "C" {
 // Largest feature dimension the built-in scratch array is sized for.  The
 // array holds PIPER_NOALLOC_MAX_STRIPS * PIPER_NOALLOC_MAX_D floats (about
 // 9.25 MiB); every GPU that loads the library reserves that much until the
-// process exits.
+// process exits.  The strip count is the fixed bound of the regular entry
+// point (two strips per SM of a 148-SM part, independent of the device), so
+// it never exceeds PIPER_NOALLOC_MAX_STRIPS.
 #define PIPER_NOALLOC_MAX_D 8192
 #define PIPER_NOALLOC_MAX_STRIPS 296
 
@@ -29,7 +31,8 @@ extern "C" {
 // pointers supplied by the caller; the work is enqueued on `stream`.
 //
 // Returns 0 on success.  Returns -1 without launching anything when D is not
-// a multiple of 8, D exceeds PIPER_NOALLOC_MAX_D, or T is negative; -2 when
+// a multiple of 8, D exceeds PIPER_NOALLOC_MAX_D, or T is negative or larger
+// than INT_MAX (rows are indexed with 32-bit ints); -2 when
 // the one-time set-up failed; -3 when a launch failed.
 // piper_noalloc_last_error() then describes the problem.
 //

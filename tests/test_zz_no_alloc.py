@@ -82,4 +82,7 @@ def test_noalloc_rejects_oversized_and_misaligned_shapes():
     assert b"exceeds" in err()
     assert fn(_ptr(t), _ptr(t), _ptr(t), _ptr(t), _ptr(t), _ptr(t), 0, 4, 12, stream) == -1
     assert b"multiple of 8" in err()
+    # more rows than the kernels' 32-bit row index can address: rejected before anything is launched
+    assert fn(_ptr(t), _ptr(t), _ptr(t), _ptr(t), _ptr(t), _ptr(t), 0, 2 ** 31, 4096, stream) == -1
+    assert b"32-bit" in err()
     torch.cuda.synchronize()

@@ -205,6 +205,10 @@ def run(args) -> dict | None:
     import torch
 
     os.environ.setdefault("CUDA_VISIBLE_DEVICES", ",".join(str(i) for i in range(max(1, torch.cuda.device_count()))))
+    # torch.distributed.run tells its workers that the launcher hosts their store; the reference's actors
+    # rendezvous among themselves (tcp:// on a port of actor 0), where rank 0 has to start the server itself
+    for var in ("TORCHELASTIC_USE_AGENT_STORE",):
+        os.environ.pop(var, None)
     # a failed replica must not leave its peers bound to an NVLink multicast object
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import ray

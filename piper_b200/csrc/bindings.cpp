@@ -13,6 +13,7 @@
 #include "elementwise.h"
 #include "gemm_sm100.h"
 #include "moe.h"
+#include "ep_exchange.h"
 #include "fused_collectives.h"
 
 namespace {

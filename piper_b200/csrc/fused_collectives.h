@@ -24,28 +24,4 @@ int f1_rs_adam_ag(const float* const* peer_grads, void* const* peer_params, uint
                   unsigned long long epoch, AdamHyper h, unsigned int* cta_counter, int* status,
                   unsigned long long timeout_ns, int num_ctas, cudaStream_t st);
 
-// Expert-parallel dispatch: writes every (token, choice) row of x [T, D] into the region that the owner of
-// its expert keeps for this source rank (peer stores), publishes the per-expert counts and a completion flag.
-// pos[t*k+j] = owner * (ep*cap) + row inside the owner's buffer.  cursor [ep*experts_local] must be zero and
-// seg_off is scratch of the same size.  Flag block layout per rank: dispatch_ready[ep], out_ready[ep].
-int ep_dispatch_push(const void* x, const int* idx, const int* counts, int* seg_off, int* cursor, int* pos,
-                     void* const* peer_recv, int* const* peer_meta, uint64_t* const* peer_flags,
-                     unsigned int* cta_counter, int my_rank, int ep, int experts_local, long long T, int D, int k,
-                     int cap, unsigned long long epoch, int num_ctas, cudaStream_t st);
-
-// Owner side: wait (bounded) for all sources, then build the group table of the regions and the flat
-// count vector [ep * experts_local].
-int ep_wait_table(const uint64_t* flags, const int* meta, int* g_start, int* g_len, int* counts_out, int ep,
-                  int experts_local, int cap, unsigned long long epoch, unsigned long long timeout_ns, int* status,
-                  cudaStream_t st);
-
-// Publishes `epoch` into slot (slot0 + my_rank) of every peer's flag block.
-int ep_signal(uint64_t* const* peer_flags, int slot0, int my_rank, int ep, unsigned long long epoch, cudaStream_t st);
-
-// Token side: out[t] = sum_j weights[t,j] * (row pos[t*k+j] of the owner's output buffer), after waiting
-// (bounded) for every owner's "outputs ready" flag.
-int ep_combine_pull(const void* const* peer_out, const int* pos, const float* weights, void* out,
-                    const uint64_t* out_flags, long long T, int D, int k, int ep, int cap, unsigned long long epoch,
-                    unsigned long long timeout_ns, int* status, int num_ctas, cudaStream_t st);
-
 }  // namespace piper

@@ -119,9 +119,20 @@ void symm_release(int64_t ptr) {
   }
 }
 
+// A tensor over memory the caller owns (a range of a symm_alloc buffer): not a view of another tensor, so it
+// can be returned from a custom op and saved by autograd like any freshly allocated tensor.
+Tensor symm_tensor_bf16(int64_t ptr, int64_t rows, int64_t cols) {
+  int dev = 0;
+  cuda_check(cudaGetDevice(&dev), "cudaGetDevice");
+  TORCH_CHECK(ptr != 0 && ptr % 16 == 0 && rows >= 0 && cols > 0, "symm_tensor_bf16: bad address or shape");
+  auto opts = at::TensorOptions().dtype(at::kBFloat16).device(at::kCUDA, dev);
+  return at::from_blob(reinterpret_cast<void*>(ptr), {rows, cols}, opts);
+}
+
 }  // namespace
 
 void register_symm_ops(torch::Library& m) {
+  m.def("symm_tensor_bf16", &symm_tensor_bf16);
   m.def("symm_alloc", &symm_alloc);
   m.def("symm_export", &symm_export);
   m.def("symm_import", &symm_import);

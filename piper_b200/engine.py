@@ -193,6 +193,10 @@ def piper_setup(model_class, model_args=(), model_kwargs: Optional[dict] = None,
     if fused_collectives:
         from .parallel.fused import FusedCollectives
         actor.fused = FusedCollectives.create(actor)
+    if dev.type == "cuda" and actor.baseline != "nccl" and os.environ.get("PIPER_FUSED", "1") != "0" \
+            and (fused_collectives or os.environ.get("PIPER_FUSED_EP") == "force"):
+        from .parallel.ep_fused import FusedExpertRuntime
+        actor.ep_fused = FusedExpertRuntime.create(actor)
     if example_inputs is not None and actor.has_first_stage():
         actor.load_input(list(example_inputs))
     if example_outputs is not None and actor.has_loss_stage():

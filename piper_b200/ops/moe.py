@@ -25,6 +25,18 @@ from .core import _is_native, _require_bf16, grad_sinks, wgrad_store
 
 PAD = 128
 
+# Set by the executor around a segment run when the expert-parallel exchanges are lowered to peer-memory kernels
+# (``parallel/ep_fused.py``): ``_EP_RUNTIME.dispatch`` replaces the local permutation of ``moe_dispatch`` by a
+# gather straight into the expert owners' receive regions, and ``_EP_TABLE`` is the group table of the receive
+# region that the expert segment reads in place.
+_EP_RUNTIME = None
+_EP_TABLE = None
+
+
+def set_ep_context(runtime, table) -> None:
+    global _EP_RUNTIME, _EP_TABLE
+    _EP_RUNTIME, _EP_TABLE = runtime, table
+
 
 def row_capacity(tokens: int, k: int, experts: int) -> int:
     """Rows a dispatch buffer needs in the worst case (every segment padded by up to PAD-1 rows)."""
@@ -95,6 +107,8 @@ def moe_group_table(counts: Tensor, expert_weights: Tensor) -> tuple[Tensor, Ten
     """
     experts = expert_weights.shape[0]
     if _is_native(counts):
+        if _EP_TABLE is not None and _EP_TABLE[0].numel() == counts.numel():
+            return _EP_TABLE[0].clone(), _EP_TABLE[1].clone()
         g_start = torch.empty_like(counts)
         g_len = torch.empty_like(counts)
         total = torch.empty(1, dtype=torch.int32, device=counts.device)
@@ -124,6 +138,8 @@ def moe_dispatch(x: Tensor, idx: Tensor, counts: Tensor) -> tuple[Tensor, Tensor
     cap = row_capacity(T, k, E)
     if _is_native(x):
         _require_bf16(x)
+        if _EP_RUNTIME is not None and _EP_RUNTIME.active is not None:
+            return _EP_RUNTIME.dispatch(x, idx, counts)
         g_start = torch.empty_like(counts)
         g_len = torch.empty_like(counts)
         total = torch.empty(1, dtype=torch.int32, device=x.device)

@@ -86,5 +86,57 @@ def check_status(device: torch.device | None = None, *, reset: bool = True) -> N
     if code != 0:
         if reset:
             t.zero_()
-        msg = STATUS_MESSAGES.get(code, f"unknown status {code}")
-        raise (PiperCommTimeout if code == 2 else PiperKernelError)(f"kernel status {code}: {msg}")
+        raise_for_status(code)
+
+
+def raise_for_status(code: int) -> None:
+    """Raise the error that status word ``code`` stands for (nothing for 0)."""
+    if code == 0:
+        return
+    msg = STATUS_MESSAGES.get(code, f"unknown status {code}")
+    raise (PiperCommTimeout if code == 2 else PiperKernelError)(f"kernel status {code}: {msg}")
+
+
+class StatusMonitor:
+    """Reads the status word once per training step without stalling the host.
+
+    ``post()`` enqueues a copy of the word into pinned host memory behind the step's work and records an
+    event; ``poll()`` (called at the start of the next step) looks at that copy once its event has completed
+    and raises ``PiperCommTimeout`` / ``PiperKernelError`` if a kernel of the earlier step gave up: a fused
+    collective that timed out has skipped its update, so training must not continue on stale replicas.
+    ``source`` defaults to the device's status word; tests pass their own tensor.
+    """
+
+    def __init__(self, device: torch.device, source: torch.Tensor | None = None) -> None:
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.source = source if source is not None else (status_tensor(self.device) if self.cuda else None)
+        self.host = torch.zeros(1, dtype=torch.int32)
+        if self.cuda:
+            self.host = self.host.pin_memory()
+        self.event = None
+        self.pending = False
+
+    def post(self) -> None:
+        if self.source is None or self.pending:
+            return
+        self.host.copy_(self.source, non_blocking=True)
+        if self.cuda:
+            self.event = torch.cuda.Event()
+            self.event.record(torch.cuda.current_stream(self.device))
+        self.pending = True
+
+    def poll(self, wait: bool = False) -> None:
+        if not self.pending:
+            return
+        if self.event is not None:
+            if wait:
+                self.event.synchronize()
+            elif not self.event.query():
+                return
+        self.pending = False
+        code = int(self.host[0])
+        if code != 0:
+            if self.source is not None:
+                self.source.zero_()
+            raise_for_status(code)

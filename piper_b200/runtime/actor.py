@@ -132,12 +132,16 @@ class PiperActor:
         self.profile_nodes = False
         self._profiler = None
         self.fused = None                   # parallel.fused.FusedCollectives when enabled
+        self.ep_fused = None                # parallel.ep_fused.FusedExpertRuntime when enabled
         self._channel_streams: dict = {}
         self._ep_splits: dict = {}          # (MB, PP, EP) -> split sizes shared by a layer's four token exchanges
         self.time_nodes = False             # debug: CUDA-event and host time per DAG node kind, in node_times
         self.last_host_time_s = 0.0
         self.activation_checkpointing = False   # forward keeps segment inputs only; backward recomputes the segment
         self.debug_keep_grads = False       # tests: keep a scaled copy of the gradients each step
+        # kernels report expired waits and rejected indices through a per-device status word; it is read once
+        # per step through pinned memory (no synchronisation) and a non-zero value of the previous step raises
+        self.status_monitor = native.StatusMonitor(device) if device.type == "cuda" else None
         self.last_grads: dict = {}
 
     # ------------------------------------------------------------ loading
@@ -256,8 +260,12 @@ class PiperActor:
     def run_dag(self, loss_fn: Callable) -> dict:
         if self.device.type == "cuda" and not self.no_nvtx:
             torch.cuda.nvtx.range_push(f"iter_{self.iteration}_rank_{self.layout.global_rank}")
+        if self.status_monitor is not None:
+            self.status_monitor.poll()
         try:
             out = DagExecutor(self).run(loss_fn)
+            if self.status_monitor is not None:
+                self.status_monitor.post()
         finally:
             if self.device.type == "cuda" and not self.no_nvtx:
                 torch.cuda.nvtx.range_pop()
@@ -529,12 +537,18 @@ class DagExecutor:
                 if t.is_floating_point():
                     t.requires_grad_(True)
             ins.append(t)
-        if a.activation_checkpointing:
-            # keep only the segment's inputs; the backward node re-runs the segment with autograd on
-            with torch.no_grad():
+        if a.ep_fused is not None:
+            a.ep_fused.enter(node)
+        try:
+            if a.activation_checkpointing:
+                # keep only the segment's inputs; the backward node re-runs the segment with autograd on
+                with torch.no_grad():
+                    outs = bucket.gm(*bucket.build_args(ins))
+            else:
                 outs = bucket.gm(*bucket.build_args(ins))
-        else:
-            outs = bucket.gm(*bucket.build_args(ins))
+        finally:
+            if a.ep_fused is not None:
+                a.ep_fused.leave()
         outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
         self.fwd_ctx[node.uid] = (ins, None if a.activation_checkpointing else outs)
         self.outs[node.uid] = outs
@@ -569,7 +583,13 @@ class DagExecutor:
         self.outs.pop(fwd_uid, None)
         if outs is None:
             # activation checkpointing: rebuild the autograd graph of this segment from its saved inputs
-            outs = bucket.gm(*bucket.build_args(ins))
+            if a.ep_fused is not None:
+                a.ep_fused.enter(self.dag.nodes[fwd_uid], replay=True)
+            try:
+                outs = bucket.gm(*bucket.build_args(ins))
+            finally:
+                if a.ep_fused is not None:
+                    a.ep_fused.leave()
             outs = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
         if split:
             ops_core.wgrad_store.begin()
@@ -607,6 +627,8 @@ class DagExecutor:
             st.absorb_autograd_grads()
         if not split and node.node_meta.get("zero_free_full_params_after") and st is not None:
             st.free_params(a.streams.get(node.stream) if self.cuda else None)
+        if a.ep_fused is not None:
+            a.ep_fused.after_node(node)
 
     def _backward_weight(self, node: TrainingDAGNode) -> None:
         a = self.a
@@ -629,6 +651,8 @@ class DagExecutor:
             st.absorb_autograd_grads()
         if node.node_meta.get("zero_free_full_params_after") and st is not None:
             st.free_params(a.streams.get(node.stream) if self.cuda else None)
+        if a.ep_fused is not None:
+            a.ep_fused.after_node(node)
 
     # ---------------------------------------------------- communication
     def _channel(self, node: TrainingDAGNode):
@@ -721,7 +745,11 @@ class DagExecutor:
         src = self.dag.data_preds(node.uid)[0]
         vals = list(self.outs[src])
         self._wait_work(src)
-        self.outs[node.uid] = exchange_tokens(self, node, vals)
+        ef = self.a.ep_fused
+        if ef is not None and ef.supports(node):
+            self.outs[node.uid] = ef.exchange(node, vals)
+        else:
+            self.outs[node.uid] = exchange_tokens(self, node, vals)
 
     def _update(self, node: TrainingDAGNode) -> None:
         a = self.a

@@ -249,3 +249,26 @@ def test_baseline_runners_dry_run_and_padded_bmm_hook():
         want[s:s + n] = (F.silu(r @ w1[e].t()) * (r @ w3[e].t())) @ w2[e].t()
         s += n
     assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_status_monitor_raises_for_the_previous_step_with_a_fake_status_word():
+    """The step driver's status check, fed by a fake status tensor: 0 passes, 2 raises the comm timeout."""
+    import pytest
+    import torch
+
+    from piper_b200.ops import native
+
+    word = torch.zeros(1, dtype=torch.int32)
+    mon = native.StatusMonitor(torch.device("cpu"), source=word)
+    mon.post()
+    mon.poll()                      # clean step: nothing raised
+    word[0] = 2                     # a fused collective gave up waiting for a peer during this step
+    mon.post()
+    with pytest.raises(native.PiperCommTimeout):
+        mon.poll()
+    assert int(word[0]) == 0        # cleared, so that the caller can decide to continue
+    word[0] = 3
+    mon.post()
+    with pytest.raises(native.PiperKernelError):
+        mon.poll(wait=True)
+    mon.poll()                      # nothing pending any more

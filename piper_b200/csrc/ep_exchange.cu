@@ -46,7 +46,7 @@ __global__ void ep_prepare_kernel(const int* __restrict__ counts, const int* __r
                                   int ep, int experts_local, int cap_src, unsigned long long timeout_ns, int* status) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   ctl[0] = 0;
-  if (!wait_flags(free_flags, ep, free_needed, timeout_ns, status)) {
+  if (!wait_flags(free_flags, ep, free_needed, timeout_ns, status, /*tag=*/1)) {
     ctl[0] = 1;
     return;
   }
@@ -154,7 +154,7 @@ __global__ void ep_wait_table_kernel(const uint64_t* __restrict__ ready_flags, c
                                      int ep, int experts_local, int cap_src, unsigned long long use,
                                      unsigned long long timeout_ns, int* status) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  const bool ok = wait_flags(ready_flags, ep, use, timeout_ns, status);
+  const bool ok = wait_flags(ready_flags, ep, use, timeout_ns, status, /*tag=*/2);
   for (int s = 0; s < ep; ++s) {
     int run = s * cap_src;
     for (int l = 0; l < experts_local; ++l) {
@@ -171,19 +171,20 @@ __global__ void ep_wait_table_kernel(const uint64_t* __restrict__ ready_flags, c
 }
 
 // Copies whole segments of rows into peers' buffers.  Segment g: rows [seg_src[g], seg_src[g] + seg_len[g]) of
-// `src` go to rank g / group_div, rows [seg_dst[g] + dst_bias, ...).  Every CTA waits (bounded) for the
-// destinations' FREE flags before its first store; the last CTA to finish publishes READY to every rank.
+// `src` go to rank g / group_div, rows [seg_dst[g] + dst_bias, ...).  The launcher puts a one-thread kernel that
+// waits for the destinations' FREE flags in front of this one (a grid of spinning CTAs would hold SMs that the
+// kernel it is waiting for may need); abort[0] != 0 means that wait ran out.  The last CTA to finish publishes
+// READY to every rank.
 __global__ void __launch_bounds__(kThreads)
 ep_block_push_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ seg_src,
                      const int* __restrict__ seg_len, const int* __restrict__ seg_dst, int num_segments, int group_div,
                      int dst_bias, long long src_rows, long long dst_rows, __nv_bfloat16* const* __restrict__ peer_dst,
-                     uint64_t* const* __restrict__ peer_flags, const uint64_t* __restrict__ free_flags,
-                     unsigned long long free_needed, int ready_off, unsigned long long use, unsigned int* cta_counter,
-                     int my_rank, int ep, int D, unsigned long long timeout_ns, int* status) {
+                     uint64_t* const* __restrict__ peer_flags, const int* __restrict__ abort, int ready_off,
+                     unsigned long long use, unsigned int* cta_counter, int my_rank, int ep, int D, int* status) {
   __shared__ int prefix[kMaxSegments + 1];     // chunks (of 32 rows) before segment g
   __shared__ int ok_s;
   if (threadIdx.x == 0) {
-    ok_s = wait_flags(free_flags, ep, free_needed, timeout_ns, status) ? 1 : 0;
+    ok_s = abort[0] == 0 ? 1 : 0;
     int run = 0;
     for (int g = 0; g < num_segments; ++g) {
       prefix[g] = run;
@@ -240,9 +241,10 @@ ep_block_push_kernel(const __nv_bfloat16* __restrict__ src, const int* __restric
 }
 
 __global__ void ep_wait_kernel(const uint64_t* __restrict__ flags, int n, unsigned long long value,
-                               unsigned long long timeout_ns, int* status) {
+                               unsigned long long timeout_ns, int* status, int tag, int* abort) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  wait_flags(flags, n, value, timeout_ns, status);
+  const bool ok = wait_flags(flags, n, value, timeout_ns, status, tag);
+  if (abort != nullptr) abort[0] = ok ? 0 : 1;
 }
 
 __global__ void ep_signal_kernel(uint64_t* const* __restrict__ peer_flags, int off, int my_rank, int ep,
@@ -277,17 +279,18 @@ int ep_wait_table(const uint64_t* ready_flags, const int* meta, int* g_start, in
 
 int ep_block_push(const EpBlockPushArgs& a, cudaStream_t st) {
   if (a.D % 8 != 0 || a.ep < 1 || a.group_div < 1 || a.num_segments < 1 || a.num_segments > kMaxSegments) return -1;
-  if (a.num_ctas < 1) return -1;
+  if (a.num_ctas < 1 || a.abort == nullptr) return -1;
+  ep_wait_kernel<<<1, 32, 0, st>>>(a.free_flags, a.ep, a.free_needed, a.timeout_ns, a.status, /*tag=*/3, a.abort);
   ep_block_push_kernel<<<a.num_ctas, kThreads, 0, st>>>(
       static_cast<const __nv_bfloat16*>(a.src), a.seg_src, a.seg_len, a.seg_dst, a.num_segments, a.group_div,
       a.dst_bias, a.src_rows, a.dst_rows, reinterpret_cast<__nv_bfloat16* const*>(a.peer_dst), a.peer_flags,
-      a.free_flags, a.free_needed, a.ready_off, a.use, a.cta_counter, a.my_rank, a.ep, a.D, a.timeout_ns, a.status);
+      a.abort, a.ready_off, a.use, a.cta_counter, a.my_rank, a.ep, a.D, a.status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 int ep_wait(const uint64_t* flags, int n, unsigned long long value, unsigned long long timeout_ns, int* status,
-            cudaStream_t st) {
-  ep_wait_kernel<<<1, 32, 0, st>>>(flags, n, value, timeout_ns, status);
+            int tag, cudaStream_t st) {
+  ep_wait_kernel<<<1, 32, 0, st>>>(flags, n, value, timeout_ns, status, tag, nullptr);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -26,9 +26,10 @@ __device__ __forceinline__ void st_release_sys(uint64_t* p, unsigned long long v
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-// Waits until flags[0..n) are all >= value.
+// Waits until flags[0..n) are all >= value.  The status word is the first of four ints: a wait that runs out
+// also leaves (tag of the wait, index of the flag it was waiting for, value it wanted) in the other three.
 __device__ inline bool wait_flags(const uint64_t* flags, int n, unsigned long long value,
-                                  unsigned long long timeout_ns, int* status) {
+                                  unsigned long long timeout_ns, int* status, int tag = 0) {
   const unsigned long long t0 = globaltimer_ns();
   for (int p = 0; p < n; ++p) {
     unsigned spins = 0;
@@ -36,7 +37,11 @@ __device__ inline bool wait_flags(const uint64_t* flags, int n, unsigned long lo
       if ((++spins & 255u) == 0) {
         if (*reinterpret_cast<volatile int*>(status) != 0) return false;
         if (globaltimer_ns() - t0 > timeout_ns) {
-          atomicCAS(status, 0, kStatusPeerTimeout);
+          if (atomicCAS(status, 0, kStatusPeerTimeout) == 0) {
+            status[1] = tag;
+            status[2] = p;
+            status[3] = static_cast<int>(value);
+          }
           return false;
         }
       }

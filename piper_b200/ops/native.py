@@ -17,6 +17,7 @@ import torch
 _LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libpiper_b200.so"
 _loaded = False
 _status: dict[int, torch.Tensor] = {}
+_status_detail: dict[int, torch.Tensor] = {}
 _cdll = None
 
 STATUS_MESSAGES = {
@@ -72,9 +73,18 @@ def status_tensor(device: torch.device | None = None) -> torch.Tensor:
     idx = dev.index if dev.index is not None else torch.cuda.current_device()
     t = _status.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
-        _status[idx] = t
+        # word 0 is the status; a peer wait that runs out leaves (tag, flag index, wanted value) in words 1..3
+        _status_detail[idx] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
+        t = _status[idx] = _status_detail[idx][:1]
     return t
+
+
+def status_detail(device: torch.device | None = None) -> list:
+    """(tag of the wait that gave up, index of the flag it waited for, value it wanted); synchronises."""
+    status_tensor(device)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    return [int(v) for v in _status_detail[idx][1:].tolist()]
 
 
 def check_status(device: torch.device | None = None, *, reset: bool = True) -> None:
@@ -84,17 +94,18 @@ def check_status(device: torch.device | None = None, *, reset: bool = True) -> N
     t = status_tensor(device)
     code = int(t.item())
     if code != 0:
+        detail = f" (wait tag, flag index, wanted value: {status_detail(device)})" if code == 2 else ""
         if reset:
             t.zero_()
-        raise_for_status(code)
+        raise_for_status(code, detail)
 
 
-def raise_for_status(code: int) -> None:
+def raise_for_status(code: int, detail: str = "") -> None:
     """Raise the error that status word ``code`` stands for (nothing for 0)."""
     if code == 0:
         return
     msg = STATUS_MESSAGES.get(code, f"unknown status {code}")
-    raise (PiperCommTimeout if code == 2 else PiperKernelError)(f"kernel status {code}: {msg}")
+    raise (PiperCommTimeout if code == 2 else PiperKernelError)(f"kernel status {code}: {msg}{detail}")
 
 
 class StatusMonitor:
@@ -137,6 +148,9 @@ class StatusMonitor:
         self.pending = False
         code = int(self.host[0])
         if code != 0:
+            detail = ""
             if self.source is not None:
+                if self.cuda and code == 2:
+                    detail = f" (wait tag, flag index, wanted value: {status_detail(self.device)})"
                 self.source.zero_()
-            raise_for_status(code)
+            raise_for_status(code, detail)

@@ -66,6 +66,10 @@ class _Exchange:
     first: int = 0                       # positions in the dispatch order between which the slot is occupied
     last: int = 0
     split_backward: bool = False         # the expert region's backward is BWD_I + BWD_W
+    gin_buf: int = 0                     # transient gradient buffers of this exchange (see _plan)
+    gret_buf: int = 0
+    gin_span: tuple = (0, 0)             # dispatch-order positions between which each is occupied
+    gret_span: tuple = (0, 0)
     # per step
     saved: Optional[tuple] = None        # outputs of the fused moe_dispatch (for an activation-checkpoint replay)
     seg_off: Any = None
@@ -74,15 +78,15 @@ class _Exchange:
     table: Optional[tuple] = None        # owner side: (g_start, g_len, recv_counts)
     recv_use: int = 0
     ret_use: int = 0
-    gin: tuple = (0, 0)                  # (ring index, use)
-    gret: tuple = (0, 0)
+    gin_use: int = 0
+    gret_use: int = 0
 
 
 class _Pool:
     """Symmetric buffers of one expert-parallel group for one problem shape."""
 
     def __init__(self, ranks: list, group, me: int, slots: int, tokens: int, dim: int, experts: int, k: int,
-                 factor: Optional[float], device: torch.device) -> None:
+                 factor: Optional[float], device: torch.device, n_gin: int = 2, n_gret: int = 2) -> None:
         lib = native.lib()
         self.ep, self.me, self.S = len(ranks), me, slots
         self.T, self.D, self.E, self.k = tokens, dim, experts, k
@@ -91,15 +95,17 @@ class _Pool:
         self.cap_own = self.ep * self.cap_src
         self.cap_loc = moe_ops.row_capacity(tokens, k, experts)
         row = dim * 2
-        self.nbuf = 2 * slots + 4
-        sizes = {"recv": slots * self.cap_own * row, "ret": slots * self.cap_loc * row, "gin": 2 * self.cap_own * row,
-                 "gret": 2 * self.cap_loc * row, "meta": slots * 2 * self.ep * self.El * 4,
+        self.n_gin, self.n_gret = n_gin, n_gret
+        self.nbuf = 2 * slots + n_gin + n_gret
+        sizes = {"recv": slots * self.cap_own * row, "ret": slots * self.cap_loc * row, "gin": n_gin * self.cap_own * row,
+                 "gret": n_gret * self.cap_loc * row, "meta": slots * 2 * self.ep * self.El * 4,
                  "flags": self.nbuf * 2 * self.ep * 8}
         self.bufs = {n: SymmetricBuffer.create(b, ranks, group) for n, b in sizes.items()}
         self.bytes = sum(sizes.values())
         self.flags_local = self.bufs["flags"].view(torch.int64, self.nbuf * 2 * self.ep)
         self.flags_ptrs = self.bufs["flags"].peer_ptrs
         self.counters = torch.zeros(self.nbuf, dtype=torch.int32, device=device)
+        self.aborts = torch.zeros(self.nbuf, dtype=torch.int32, device=device)
         self.uses = [0] * self.nbuf
 
         def ptrs(name, i, stride):
@@ -111,13 +117,13 @@ class _Pool:
 
         self.recv_ptrs = [ptrs("recv", s, self.cap_own * row) for s in range(slots)]
         self.ret_ptrs = [ptrs("ret", s, self.cap_loc * row) for s in range(slots)]
-        self.gin_ptrs = [ptrs("gin", r, self.cap_own * row) for r in range(2)]
-        self.gret_ptrs = [ptrs("gret", r, self.cap_loc * row) for r in range(2)]
+        self.gin_ptrs = [ptrs("gin", r, self.cap_own * row) for r in range(n_gin)]
+        self.gret_ptrs = [ptrs("gret", r, self.cap_loc * row) for r in range(n_gret)]
         self.meta_ptrs = [ptrs("meta", s, 2 * self.ep * self.El * 4) for s in range(slots)]
         self.recv = [local("recv", s, self.cap_own) for s in range(slots)]
         self.ret = [local("ret", s, self.cap_loc) for s in range(slots)]
-        self.gin = [local("gin", r, self.cap_own) for r in range(2)]
-        self.gret = [local("gret", r, self.cap_loc) for r in range(2)]
+        self.gin = [local("gin", r, self.cap_own) for r in range(n_gin)]
+        self.gret = [local("gret", r, self.cap_loc) for r in range(n_gret)]
         G2 = 2 * self.ep * self.El
         meta_all = self.bufs["meta"].view(torch.int32, slots * G2)
         self.meta = [meta_all[s * G2:(s + 1) * G2] for s in range(slots)]
@@ -125,9 +131,9 @@ class _Pool:
         if self.ep > 1:
             dist.barrier(group=group)
 
-    # buffer numbering: recv slots, ret slots, gin ring, gret ring
+    # buffer numbering: recv slots, ret slots, incoming-gradient buffers, returned-gradient buffers
     def buf_id(self, kind: str, i: int) -> int:
-        return {"recv": 0, "ret": self.S, "gin": 2 * self.S, "gret": 2 * self.S + 2}[kind] + i
+        return {"recv": 0, "ret": self.S, "gin": 2 * self.S, "gret": 2 * self.S + self.n_gin}[kind] + i
 
     def off(self, b: int, which: int) -> int:
         return (b * 2 + which) * self.ep
@@ -152,8 +158,7 @@ class FusedExpertRuntime:
         self.region_of: dict[str, tuple] = {}     # forward node of the expert region -> key
         self.after: dict[str, list] = {}          # compute uid -> [(action, key)] run after the node
         self.pool: Optional[_Pool] = None
-        self.slots = 0
-        self.ring = {"gin": 0, "gret": 0}
+        self.slots = self.n_gin = self.n_gret = 0
         self.active: Optional[_Exchange] = None   # exchange whose moe_dispatch the running segment contains
         self.replay = False
         self._plan()
@@ -227,29 +232,25 @@ class FusedExpertRuntime:
                             last = dag.nodes[u]
                 self.after.setdefault(last.uid, []).append(("free_recv", key))
                 x.last = max(x.last, index[last.uid])
+                # a split backward copies the incoming gradients out at once, so their buffer is free again
+                x.gin_span = (index[n.uid], index[n.uid] if x.split_backward else index[succ.uid])
             else:
                 self.role[n.uid] = ("B_out", key)
                 self.after.setdefault(succ.uid, []).append(("free_gret", key))
-        # slots: greedy colouring of the occupancy intervals in dispatch order (identical on every rank of the
-        # group, because they replay the same order)
-        free: list[int] = []
-        busy: list[tuple] = []
-        nslots = 0
-        for x in sorted(self.exchanges.values(), key=lambda e: e.first):
+                x.gret_span = (index[n.uid], index[succ.uid])
+        # Buffers are handed out by greedy colouring of the occupancy intervals in dispatch order (identical on
+        # every rank of the group, because they replay the same order).  A buffer is reused only by an exchange
+        # that starts after the node that frees it, so every FREE flag a kernel waits for is set by work that this
+        # rank (and, by the common order, every peer) enqueued earlier: no wait depends on a later launch.
+        xs = list(self.exchanges.values())
+        for x in xs:
             if x.last <= x.first:
                 x.last = len(order)            # forward-only plan: the slot is never handed back within a step
-            for item in sorted(busy):
-                if item[0] < x.first:
-                    busy.remove(item)
-                    free.append(item[1])
-            if free:
-                x.slot = min(free)
-                free.remove(x.slot)
-            else:
-                x.slot = nslots
-                nslots += 1
-            busy.append((x.last, x.slot))
-        self.slots = nslots
+        self.slots = _colour([(x.first, x.last) for x in xs], lambda i, c: setattr(xs[i], "slot", c))
+        back = [x for x in xs if x.gin_span != (0, 0)]
+        self.n_gin = max(1, _colour([x.gin_span for x in back], lambda i, c: setattr(back[i], "gin_buf", c)))
+        back = [x for x in xs if x.gret_span != (0, 0)]
+        self.n_gret = max(1, _colour([x.gret_span for x in back], lambda i, c: setattr(back[i], "gret_buf", c)))
 
     # --------------------------------------------------------------- segment hooks
     def enter(self, node, replay: bool = False) -> None:
@@ -277,9 +278,9 @@ class FusedExpertRuntime:
             elif action == "free_recv":
                 self._signal(p.buf_id("recv", x.slot), x.recv_use)
                 if not x.split_backward:
-                    self._signal(p.buf_id("gin", x.gin[0]), x.gin[1])
+                    self._signal(p.buf_id("gin", x.gin_buf), x.gin_use)
             elif action == "free_gret":
-                self._signal(p.buf_id("gret", x.gret[0]), x.gret[1])
+                self._signal(p.buf_id("gret", x.gret_buf), x.gret_use)
 
     def _signal(self, b: int, value: int) -> None:
         p = self.pool
@@ -296,9 +297,11 @@ class FusedExpertRuntime:
         T, D = x.shape
         k, E = idx.shape[1], counts.numel()
         if self.pool is None:
-            self.pool = _Pool(self.ranks, self.group, self.me, self.slots, T, D, E, k, self.factor, dev)
-            logger.info("expert exchange: %d slots, %d rows per source region, %.2f GB of symmetric memory",
-                        self.slots, self.pool.cap_src, self.pool.bytes / 2 ** 30)
+            self.pool = _Pool(self.ranks, self.group, self.me, self.slots, T, D, E, k, self.factor, dev, self.n_gin,
+                              self.n_gret)
+            logger.info("expert exchange: %d slots, %d + %d gradient buffers, %d rows per source region, %.2f GB of "
+                        "symmetric memory", self.slots, self.n_gin, self.n_gret, self.pool.cap_src,
+                        self.pool.bytes / 2 ** 30)
         p = self.pool
         if (T, D, E, k) != (p.T, p.D, p.E, p.k):
             raise ValueError(f"expert exchange buffers were sized for tokens={p.T} dim={p.D} experts={p.E} k={p.k}, "
@@ -353,32 +356,32 @@ class FusedExpertRuntime:
         rows = vals[ti].contiguous()
         if kind in ("F_out", "B_out"):
             # expert owner -> token owners: segment (source, local expert) goes home to the source's own layout
-            name, i = ("ret", ex.slot) if kind == "F_out" else ("gret", self._next_ring("gret"))
+            name, i = ("ret", ex.slot) if kind == "F_out" else ("gret", ex.gret_buf)
             b = p.buf_id(name, i)
             use = p.next_use(b)
             dst = p.ret_ptrs[i] if kind == "F_out" else p.gret_ptrs[i]
             g_start, g_len, _ = ex.table
             lib.ep_block_push(rows, g_start, g_len, p.meta[ex.slot][G:2 * G], p.El, 0, p.cap_loc, dst, p.flags_ptrs,
                               p.flags_local, p.off(b, FREE), self._free_needed(b, use), p.off(b, READY), use,
-                              p.counters[b:b + 1], self.me, self.ep, self.timeout_s, status, self.num_ctas)
-            lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status)
+                              p.counters[b:b + 1], p.aborts[b:b + 1], self.me, self.ep, self.timeout_s, status, self.num_ctas)
+            lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 4 if kind == "F_out" else 6)
             if kind == "F_out":
                 ex.ret_use = use
                 out[ti] = p.ret[i]
             else:
-                ex.gret = (i, use)
+                ex.gret_use = use
                 out[ti] = p.gret[i]
             return tuple(out)
         # B_in: token owner -> expert owners, the local padded segments land where the forward rows landed
-        i = self._next_ring("gin")
+        i = ex.gin_buf
         b = p.buf_id("gin", i)
         use = p.next_use(b)
         lib.ep_block_push(rows, ex.g_start_loc, ex.g_len_loc, ex.seg_off, p.El, self.me * p.cap_src, p.cap_own,
                           p.gin_ptrs[i], p.flags_ptrs, p.flags_local, p.off(b, FREE), self._free_needed(b, use),
-                          p.off(b, READY), use, p.counters[b:b + 1], self.me, self.ep, self.timeout_s, status,
-                          self.num_ctas)
-        lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status)
-        ex.gin = (i, use)
+                          p.off(b, READY), use, p.counters[b:b + 1], p.aborts[b:b + 1], self.me, self.ep,
+                          self.timeout_s, status, self.num_ctas)
+        lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 5)
+        ex.gin_use = use
         if ex.split_backward:
             # the deferred weight-gradient GEMMs read these rows long after the ring has moved on
             out[ti] = p.gin[i].clone()
@@ -387,13 +390,31 @@ class FusedExpertRuntime:
             out[ti] = p.gin[i]
         return tuple(out)
 
-    def _next_ring(self, name: str) -> int:
-        self.ring[name] ^= 1
-        return self.ring[name]
-
     @staticmethod
     def _free_needed(b: int, use: int) -> int:
         return use - 1
+
+
+def _colour(spans: list, assign) -> int:
+    """Greedy interval colouring: span i gets the lowest colour whose previous span ended before it starts."""
+    free: list[int] = []
+    busy: list[tuple] = []
+    n = 0
+    for i in sorted(range(len(spans)), key=lambda j: spans[j][0]):
+        lo, hi = spans[i]
+        for item in sorted(busy):
+            if item[0] < lo:
+                busy.remove(item)
+                free.append(item[1])
+        if free:
+            c = min(free)
+            free.remove(c)
+        else:
+            c = n
+            n += 1
+        assign(i, c)
+        busy.append((hi, c))
+    return n
 
 
 def _same_host(group) -> bool:

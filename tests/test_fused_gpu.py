@@ -272,7 +272,7 @@ def test_expert_dispatch_rejects_a_region_overflow():
     from piper_b200.parallel.ep_fused import _Pool
 
     dev = torch.device("cuda")
-    T, D, E, k = 256, 128, 4, 2
+    T, D, E, k = 1024, 128, 4, 2
     pool = _Pool([0], None, 0, 1, T, D, E, k, 0.25, dev)       # a quarter of the balanced share
     assert pool.cap_src < T * k
     x = torch.randn(T, D, device=dev).to(torch.bfloat16)

@@ -14,7 +14,7 @@
 #include "gemm_sm100.h"
 #include "moe.h"
 #include "ep_exchange.h"
-#include "fused_collectives.h"
+#include "zero_fused.h"
 
 namespace {
 
@@ -225,7 +225,7 @@ void ce_bwd(const Tensor& logits, const Tensor& labels, const Tensor& lse, const
 }
 
 void adam_flat(Tensor master, Tensor m, Tensor v, const Tensor& grad, const OptTensor& param_bf16, double lr,
-               double b1, double b2, double eps, double wd, int64_t step, double grad_scale) {
+               double b1, double b2, double eps, double wd, int64_t step, double grad_scale, bool decoupled) {
   TORCH_CHECK(master.scalar_type() == at::kFloat && grad.scalar_type() == at::kFloat, "adam buffers are fp32");
   TORCH_CHECK(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous(),
               "adam buffers must be contiguous");
@@ -233,7 +233,8 @@ void adam_flat(Tensor master, Tensor m, Tensor v, const Tensor& grad, const OptT
                             grad.data_ptr<float>(), param_bf16.has_value() ? param_bf16->data_ptr() : nullptr,
                             master.numel(), static_cast<float>(lr), static_cast<float>(b1),
                             static_cast<float>(b2), static_cast<float>(eps), static_cast<float>(wd),
-                            static_cast<int>(step), static_cast<float>(grad_scale), cur_stream()),
+                            static_cast<int>(step), static_cast<float>(grad_scale), decoupled ? 1 : 0,
+                            cur_stream()),
            "adam_flat");
 }
 

@@ -737,22 +737,25 @@ ce_bwd_kernel(const __nv_bfloat16* __restrict__ logits, const long long* __restr
 }
 
 // --------------------------------------------------------------------- Adam
-// Flat-buffer Adam(W): fp32 master / m / v, fp32 gradient (scaled by
-// grad_scale), bf16 parameter copy written in the same pass.
+// Flat-buffer Adam / AdamW: fp32 master / m / v, fp32 gradient (scaled by
+// grad_scale), bf16 parameter copy written in the same pass.  decoupled != 0
+// is AdamW (the decay shrinks the weight directly); otherwise the decay is
+// the L2 term of torch.optim.Adam, added to the gradient before the moments.
 __global__ void adam_flat_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                                  const float* __restrict__ grad, __nv_bfloat16* __restrict__ param,
                                  long long n, float lr, float b1, float b2, float eps, float wd,
-                                 float bc1, float bc2, float grad_scale) {
+                                 float bc1, float bc2, float grad_scale, int decoupled) {
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float g = grad[i] * grad_scale;
     float p = master[i];
+    float g = grad[i] * grad_scale;
+    if (!decoupled) g += wd * p;
     const float mi = b1 * m[i] + (1.f - b1) * g;
     const float vi = b2 * v[i] + (1.f - b2) * g * g;
     m[i] = mi;
     v[i] = vi;
     const float denom = sqrtf(vi / bc2) + eps;
-    p = p - lr * (mi / bc1) / denom - lr * wd * p;
+    p = p - lr * (mi / bc1) / denom - (decoupled ? lr * wd * p : 0.f);
     master[i] = p;
     if (param) param[i] = __float2bfloat16(p);
   }
@@ -983,14 +986,14 @@ int ce_bwd(const void* logits, const long long* labels, const float* lse, const 
 }
 
 int adam_flat(float* master, float* m, float* v, const float* grad, void* param_bf16, long long n,
-              float lr, float b1, float b2, float eps, float wd, int step, float grad_scale,
+              float lr, float b1, float b2, float eps, float wd, int step, float grad_scale, int decoupled,
               cudaStream_t st) {
   if (n == 0) return 0;
   const float bc1 = 1.f - powf(b1, static_cast<float>(step));
   const float bc2 = 1.f - powf(b2, static_cast<float>(step));
   adam_flat_kernel<<<grid_for(n, 256), 256, 0, st>>>(master, m, v, grad,
                                                     static_cast<__nv_bfloat16*>(param_bf16), n, lr, b1, b2,
-                                                    eps, wd, bc1, bc2, grad_scale);
+                                                    eps, wd, bc1, bc2, grad_scale, decoupled);
   return PIPER_LAUNCH_OK();
 }
 

@@ -48,7 +48,7 @@ int ce_bwd(const void* logits, const long long* labels, const float* lse, const 
            cudaStream_t st);
 
 int adam_flat(float* master, float* m, float* v, const float* grad, void* param_bf16, long long n,
-              float lr, float b1, float b2, float eps, float wd, int step, float grad_scale,
+              float lr, float b1, float b2, float eps, float wd, int step, float grad_scale, int decoupled,
               cudaStream_t st);
 int cast_f32_to_bf16(const float* in, void* out, long long n, float scale, cudaStream_t st);
 int add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t st);

@@ -289,8 +289,8 @@ int ep_block_push(const EpBlockPushArgs& a, cudaStream_t st) {
 }
 
 int ep_wait(const uint64_t* flags, int n, unsigned long long value, unsigned long long timeout_ns, int* status,
-            int tag, cudaStream_t st) {
-  ep_wait_kernel<<<1, 32, 0, st>>>(flags, n, value, timeout_ns, status, tag, nullptr);
+            int tag, int* abort, cudaStream_t st) {
+  ep_wait_kernel<<<1, 32, 0, st>>>(flags, n, value, timeout_ns, status, tag, abort);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -67,9 +67,10 @@ struct EpBlockPushArgs {
 // Copies row segments into peers' buffers (segment g to rank g / group_div) and publishes READY.
 int ep_block_push(const EpBlockPushArgs& a, cudaStream_t st);
 
-// One-thread kernels: wait until flags[0..n) >= value (`tag` is reported if the wait runs out); store value into word (off + my_rank) of every rank.
+// One-thread kernels: wait until flags[0..n) >= value (`tag` is reported if the wait runs out;
+// abort[0], if given, becomes 1 then and 0 otherwise); store value into word (off + my_rank) of every rank.
 int ep_wait(const uint64_t* flags, int n, unsigned long long value, unsigned long long timeout_ns, int* status,
-            int tag, cudaStream_t st);
+            int tag, int* abort, cudaStream_t st);
 int ep_signal(uint64_t* const* peer_flags, int off, int my_rank, int ep, unsigned long long value, cudaStream_t st);
 
 }  // namespace piper

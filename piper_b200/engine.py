@@ -72,19 +72,46 @@ def _bind_channels(dag: TrainingDAG, dp_rank: int) -> None:
 
 
 def _adam_config(optim_fn, optim_kwargs: Optional[dict]) -> AdamConfig:
-    kw = dict(optim_kwargs or {})
-    cfg = AdamConfig()
-    if "lr" in kw:
-        cfg.lr = float(kw["lr"])
-    if "betas" in kw:
-        cfg.betas = tuple(kw["betas"])
-    if "eps" in kw:
-        cfg.eps = float(kw["eps"])
-    if "weight_decay" in kw:
-        cfg.weight_decay = float(kw["weight_decay"])
-    if optim_fn is not None and optim_fn not in (torch.optim.Adam, torch.optim.AdamW):
-        logger.warning("optim_fn=%s is not Adam/AdamW; the flat fused Adam update is used with its hyper-parameters",
-                       getattr(optim_fn, "__name__", optim_fn))
+    """Hyper-parameters of the flat Adam / AdamW kernels from the reference's ``optim_fn`` argument.
+
+    The reference instantiates ``optim_class(params)`` per bucket (``src/actor.py:573,600``).  Here the update is
+    one kernel over flat buffers, so only ``torch.optim.Adam`` (L2 decay added to the gradient) and
+    ``torch.optim.AdamW`` (decoupled decay) can be honoured; ``optim_fn`` may be the class, a
+    ``functools.partial`` of it, or ``None`` (Adam).  Anything the kernels cannot reproduce is rejected.
+    """
+    import functools
+
+    kw: dict = {}
+    fn = optim_fn
+    while isinstance(fn, functools.partial):
+        kw = {**fn.keywords, **kw}
+        if fn.args:
+            raise ValueError("optim_fn: positional arguments of a functools.partial are not supported")
+        fn = fn.func
+    kw.update(optim_kwargs or {})
+    if fn is None:
+        fn = torch.optim.Adam
+    if fn not in (torch.optim.Adam, torch.optim.AdamW):
+        raise ValueError(f"optim_fn={getattr(fn, '__name__', fn)!r}: the flat optimizer kernels implement "
+                         "torch.optim.Adam and torch.optim.AdamW only")
+    cfg = AdamConfig(decoupled=fn is torch.optim.AdamW)
+    if fn is torch.optim.AdamW and "weight_decay" not in kw:
+        cfg.weight_decay = 1e-2                     # torch.optim.AdamW's default
+    for k, v in kw.items():
+        if k == "lr":
+            cfg.lr = float(v)
+        elif k == "betas":
+            cfg.betas = (float(v[0]), float(v[1]))
+        elif k == "eps":
+            cfg.eps = float(v)
+        elif k == "weight_decay":
+            cfg.weight_decay = float(v)
+        elif k in ("fused", "foreach", "capturable", "differentiable"):
+            continue                                # implementation switches of torch.optim, no effect on the math
+        elif k in ("amsgrad", "maximize") and not v:
+            continue
+        else:
+            raise ValueError(f"optimizer argument {k}={v!r} is not supported by the flat Adam/AdamW kernels")
     return cfg
 
 

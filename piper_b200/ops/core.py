@@ -93,6 +93,11 @@ class WgradStore:
 
 wgrad_store = WgradStore()
 
+# ZeRO-3 with the fused lowering: weight address -> launcher of the GEMM that gathers that weight's rows from the
+# data-parallel peers while it multiplies by them (registered by ``parallel/fused.py`` when the parameters of a
+# segment are materialised, consumed by the first ``linear`` that uses the weight).
+gather_gemms: dict = {}
+
 
 def _is_native(t: Tensor) -> bool:
     return t.is_cuda
@@ -123,7 +128,11 @@ def linear(x: Tensor, w: Tensor) -> Tensor:
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         y = torch.empty((x2.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
-        _gemm(x2, w, y, False, False)
+        fused_gather = gather_gemms.pop(w.data_ptr(), None) if gather_gemms else None
+        if fused_gather is not None:
+            fused_gather(x2, y)
+        else:
+            _gemm(x2, w, y, False, False)
         return y.view(*x.shape[:-1], w.shape[0])
     return torch.nn.functional.linear(x, w)
 

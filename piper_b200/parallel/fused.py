@@ -1,13 +1,34 @@
 """Fused compute+collective paths used by the executor instead of NCCL calls.
 
-``FusedCollectives`` moves a data-parallel bucket's fp32 gradient buffer and bf16 parameter buffer into
-symmetric memory and replaces ``all_reduce(grads)`` + ``Adam`` by one kernel per bucket
-(``csrc/fused_collectives.cu``): reduce-scatter over peer loads, sharded Adam, all-gather by peer stores.
-The optimizer state of such a bucket is sharded over the data-parallel group (each rank keeps fp32 master
-weights and moments for 1/dp of the bucket), which is what cuts the update's HBM traffic and memory by dp.
+``FusedCollectives`` adopts every data-parallel bucket of the actor (plain ``replicate``, ``shard_grads``,
+``shard_params``) and replaces the collectives of its gradient and parameter life cycle by kernels that read and
+write the peers' memory (``csrc/zero_fused.cu``, ``csrc/ag_gemm_sm100.cu``):
 
-The NCCL lowering (``ParamStorage.all_reduce_grads`` + the flat Adam kernel) stays available as the
-baseline; ``PIPER_FUSED=0`` or ``piper_setup(fused_collectives=False)`` selects it.
+============================ ============================================== ==================================
+reference call site           NCCL lowering (``PIPER_FUSED=0``)              fused lowering
+============================ ============================================== ==================================
+``all_reduce(grad)`` per      ``all_reduce`` of the flat bucket + local Adam  one kernel: reduce-scatter by peer
+tensor, ``src/executors.py``  on the whole bucket                             loads, Adam on this rank's rows,
+``:125-127``                                                                  new bf16 rows stored into every
+                                                                              rank's parameter buffer
+``reduce_scatter_tensor`` +   the same two calls + Adam on the shard at the   the same kernel per gradient chain,
+``add_``, ``:150-154``        end of the step (+ all-gather for ZeRO-2)       accumulating into the fp32 shard;
+                                                                              Adam fused into the last one
+``all_gather_into_tensor``,   ``all_gather_into_tensor`` into the full        pull kernel over the peers' shards;
+``src/runtime.py:443``        buffer                                          the first weight a forward segment
+                                                                              multiplies by is gathered inside
+                                                                              that GEMM (``ag_gemm``)
+============================ ============================================== ==================================
+
+Buckets are sharded by parameter rows (``ParamStorage.row_layout``): rank ``p`` keeps fp32 master weights, Adam
+moments and a gradient accumulator for piece ``p`` of every parameter, which cuts the update's memory and HBM
+traffic by ``dp`` also for plain ``replicate`` buckets.  Gradient buffers (and, unless parameters are sharded,
+the parameter buffers) live in symmetric memory.
+
+Neither kernel spins: each is bracketed by one-thread kernels that publish and wait for flag words (READY: "my
+gradients of this reduction are final"; DONE: "I have read everybody's gradients and stored my update";
+PARAMS: "my shard holds version v").  A wait that runs out records ``kStatusPeerTimeout``, the kernel behind it
+does nothing, and the step driver raises ``PiperCommTimeout`` at the next step.
 """
 from __future__ import annotations
 
@@ -25,15 +46,55 @@ from .symm import SymmetricBuffer
 
 logger = create_logger("piper_fused", LOG_LEVEL)
 
+READY_OFF, DONE_OFF, PARAMS_OFF = 0, 1, 2          # flag blocks of dp words each
+
+
+def first_linear_slot(gm, slot_positions: list) -> int:
+    """Index (into ``slot_positions``) of the weight that the segment's first ``piper::linear`` multiplies by, if
+    that call is also the first use of the weight; -1 otherwise."""
+    phs = [n for n in gm.graph.nodes if n.op == "placeholder"]
+    pos_of = {n: i for i, n in enumerate(phs)}
+    for n in gm.graph.nodes:
+        if n.op != "call_function" or "piper.linear" not in str(n.target).replace("::", "."):
+            continue
+        w = n.args[1] if len(n.args) > 1 else None
+        if w in pos_of and pos_of[w] in slot_positions:
+            users = sorted(w.users, key=lambda u: list(gm.graph.nodes).index(u))
+            if users and users[0] is n and len(users) == 1:
+                return slot_positions.index(pos_of[w])
+        return -1
+    return -1
+
 
 class _FusedBucket:
-    def __init__(self, st: ParamStorage, buf: SymmetricBuffer, grads_off: int, flags_off: int) -> None:
-        self.buf = buf
-        self.peer_params = buf.offset_ptrs(0)
-        self.peer_grads = buf.offset_ptrs(grads_off)
-        self.peer_flags = buf.offset_ptrs(flags_off)
-        self.counter = torch.zeros(1, dtype=torch.int32, device=st.device)
-        self.epoch = 0
+    def __init__(self, st: ParamStorage, ranks: list, group, dp: int) -> None:
+        dev = st.device
+        self.st = st
+        table, shard = ParamStorage.row_layout(st.slots, dp)
+        self.shard_numel = shard
+        self.bufs: dict[str, SymmetricBuffer] = {}
+
+        def symm(name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+            esz = torch.empty((), dtype=dtype).element_size()
+            self.bufs[name] = SymmetricBuffer.create(numel * esz, ranks, group)
+            return self.bufs[name].view(dtype, numel)
+
+        self.flags_local = symm("flags", 3 * dp, torch.int64)
+        self.full_grads = symm("grads", st.numel, torch.float32)
+        self.full_params = None if st.params_sharded else symm("params", st.numel, st.dtype)
+        self.alloc = symm
+        t = torch.tensor([[s.offset for s in st.slots], [sh for sh, _ in table], [stride for _, stride in table],
+                          [(s.numel + 63) // 64 * 64 for s in st.slots]], dtype=torch.int64)
+        self.table = t.to(dev)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.abort = torch.zeros(2, dtype=torch.int32, device=dev)      # [reduce, gather]
+        self.scratch: Optional[torch.Tensor] = None                      # bookkeeping of the gather GEMM
+        self.use = 0
+        self.version = 0
+        self.first_slot = -1
+
+    def ptrs(self, name: str) -> torch.Tensor:
+        return self.bufs[name].peer_ptrs
 
 
 class FusedCollectives:
@@ -47,52 +108,118 @@ class FusedCollectives:
     def create(cls, actor) -> Optional["FusedCollectives"]:
         if actor.device.type != "cuda" or actor.groups is None or actor.layout.dp_degree <= 1:
             return None
+        if not _same_host(actor.groups.dp_group):
+            logger.warning("data-parallel group spans hosts: peer memory is unavailable, using the NCCL lowering")
+            return None
         self = cls(actor, float(os.environ.get("PIPER_PEER_TIMEOUT_S", "30")),
                    int(os.environ.get("PIPER_F1_CTAS", "128")))
         for b in actor.buckets.values():
             st = b.storage
-            if st is not None and st.mode == "allreduce" and st.numel > 0 and st.dtype == torch.bfloat16:
-                self._adopt(st)
+            if st is not None and st.mode in ("allreduce", "zero2", "zero3") and st.numel > 0 \
+                    and st.dtype == torch.bfloat16:
+                self._adopt(st, b)
         return self
 
-    def _adopt(self, st: ParamStorage) -> None:
-        """Re-home the bucket's parameter and gradient buffers in symmetric memory and shard its Adam state."""
+    def _adopt(self, st: ParamStorage, bucket) -> None:
+        """Re-home the bucket's gradient (and parameter) buffers in symmetric memory and re-shard its state by rows."""
         lay = self.actor.layout
-        p_bytes = st.numel * 2
-        g_off = (p_bytes + 255) // 256 * 256
-        f_off = g_off + st.numel * 4
-        buf = SymmetricBuffer.create(f_off + 2 * 8 * lay.dp_degree, list(lay.dp_ranks), self.actor.groups.dp_group)
-        new_params = buf.view(torch.bfloat16, st.numel, 0)
-        new_grads = buf.view(torch.float32, st.numel, g_off)
-        new_params.copy_(st.flat_params)
+        fb = _FusedBucket(st, list(lay.dp_ranks), self.actor.groups.dp_group, lay.dp_degree)
+        st.convert_to_rows(fb.alloc)                    # reads the current parameters (gathers them if sharded)
         st._unregister_sinks()
-        st.flat_params = new_params
-        st.flat_grads = new_grads
-        st._bind(new_params)
-        st._register_sinks()
-        lo, hi = lay.dp_rank * st.shard_numel, (lay.dp_rank + 1) * st.shard_numel
-        st.master = st.master[lo:hi].clone()
-        st.m = st.m[lo:hi].clone()
-        st.v = st.v[lo:hi].clone()
-        st.shard_params = new_params[lo:hi]
-        st.fused_shard = (lo, hi)
-        self.buckets[st.key] = _FusedBucket(st, buf, g_off, f_off)
+        if fb.full_params is not None:
+            fb.full_params.copy_(st.flat_params)
+            st.flat_params = fb.full_params
+            st._bind(fb.full_params)
+        st.flat_grads = fb.full_grads
+        st.persistent_grads = True
+        if st.params_live:
+            st._register_sinks()
+        slot_pos = [s.pos for s in st.slots]
+        fb.first_slot = first_linear_slot(bucket.gm, slot_pos) if st.params_sharded else -1
+        if fb.first_slot >= 0:
+            n_rows = st.slots[fb.first_slot].shape[0]
+            fb.scratch = torch.zeros((n_rows + 255) // 256 + 2, dtype=torch.int32, device=st.device)
+        self.buckets[st.key] = fb
         torch.cuda.synchronize()
         dist.barrier(group=self.actor.groups.dp_group)
 
     def supports(self, st: ParamStorage) -> bool:
-        return st.key in self.buckets
+        return st is not None and st.key in self.buckets
 
-    def reduce_scatter_adam(self, st: ParamStorage, grad_scale: float) -> None:
+    # ------------------------------------------------------------------ gradients
+    def reduce(self, st: ParamStorage, final: bool, grad_scale: float) -> None:
+        """Reduce-scatter the group's gradient buckets into this rank's shard; with ``final`` also the optimizer
+        step and the publication of the new parameters.  Runs on the current stream."""
         fb = self.buckets[st.key]
-        fb.epoch += 1
-        st.step_count += 1
-        a = st.adam
-        lay = self.actor.layout
-        native.lib().f1_rs_adam_ag(fb.peer_grads, fb.peer_params, fb.peer_flags, st.master, st.m, st.v, lay.dp_rank,
-                                   lay.dp_degree, fb.epoch, a.lr, a.betas[0], a.betas[1], a.eps, a.weight_decay,
-                                   st.step_count, grad_scale, fb.counter, native.status_tensor(st.device),
-                                   self.timeout_s, self.num_ctas)
+        lib, lay, a = native.lib(), self.actor.layout, st.adam
+        dp, me = lay.dp_degree, lay.dp_rank
+        status = native.status_tensor(st.device)
+        fb.use += 1
+        flags = fb.ptrs("flags")
+        lib.ep_signal(flags, READY_OFF * dp, me, dp, fb.use)
+        lib.ep_wait(fb.flags_local, READY_OFF * dp, dp, fb.use, self.timeout_s, status, 11, fb.abort[0:1])
+        if final:
+            st.step_count += 1
+        accumulate = st.mode != "allreduce"
+        lib.zero_reduce(fb.ptrs("grads"), st.shard_grads if accumulate else None, st.master, st.m, st.v,
+                        st.shard_params, None if st.params_sharded else fb.ptrs("params"), fb.table, me, dp,
+                        accumulate, final, a.lr, a.betas[0], a.betas[1], a.eps, a.weight_decay, a.decoupled,
+                        max(st.step_count, 1), grad_scale, flags, DONE_OFF * dp, fb.use, fb.counter, fb.abort[0:1],
+                        self.num_ctas)
+        # nobody reads this rank's gradients any more once every peer is done: clear them for the next chain
+        lib.ep_wait(fb.flags_local, DONE_OFF * dp, dp, fb.use, self.timeout_s, status, 12, None)
+        st.flat_grads.zero_()
+        if final:
+            st.fused_stepped = True
+            if st.params_sharded:
+                fb.version += 1
+                lib.ep_signal(flags, PARAMS_OFF * dp, me, dp, fb.version)
+
+    # ----------------------------------------------------------------- parameters
+    def gather(self, st: ParamStorage, fuse_first: bool) -> None:
+        """ZeRO-3 parameter materialisation on the current stream: pull every peer's rows into the full buffer;
+        with ``fuse_first`` the first linear weight of the segment is left to the GEMM that multiplies by it."""
+        if st.numel == 0:
+            return
+        st.param_users += 1
+        if st.params_live:
+            return
+        fb = self.buckets[st.key]
+        lib, lay = native.lib(), self.actor.layout
+        dp = lay.dp_degree
+        st.flat_params.untyped_storage().resize_(st.numel * st.flat_params.element_size())
+        status = native.status_tensor(st.device)
+        lib.ep_wait(fb.flags_local, PARAMS_OFF * dp, dp, fb.version, self.timeout_s, status, 13, fb.abort[1:2])
+        skip = fb.first_slot if (fuse_first and fb.first_slot >= 0) else -1
+        lib.zero_gather(fb.ptrs("shard_params"), st.flat_params, fb.table, dp, skip, fb.abort[1:2], self.num_ctas)
+        st.params_live = True
+        st._register_sinks()
+        if skip >= 0:
+            s = st.slots[skip]
+            w = st.param_views[s.pos]
+            sh, stride = st.row_table[skip]
+            k = s.numel // s.shape[0]
+            shard_ptrs = [int(p) + sh * 2 for p in fb.bufs["shard_params"].ptrs]
+            w_full = st.flat_params[s.offset:s.offset + s.numel].view(s.shape[0], k)
+
+            def run(x2: torch.Tensor, y: torch.Tensor, fb=fb, me=lay.dp_rank, rows=stride // k, n=s.shape[0]) -> None:
+                lib.ag_gemm(x2, shard_ptrs, me, w_full, fb.scratch, y, n, rows, native.status_tensor(x2.device))
+
+            ops_core.gather_gemms[w.data_ptr()] = run
+
+    def release(self, st: ParamStorage) -> None:
+        """The full buffer is about to be freed: a gather GEMM that never ran must not fire on a later tensor."""
+        fb = self.buckets.get(st.key)
+        if fb is not None and fb.first_slot >= 0 and st.params_live:
+            w = st.param_views[st.slots[fb.first_slot].pos]
+            ops_core.gather_gemms.pop(w.data_ptr(), None)
+
+
+def _same_host(group) -> bool:
+    import socket
+    names: list = [None] * dist.get_world_size(group)
+    dist.all_gather_object(names, socket.gethostname(), group=group)
+    return len(set(names)) == 1
 
 
 # --------------------------------------------------------------------------------------------------
@@ -134,70 +261,3 @@ class ShardedWeight:
         native.lib().ag_gemm(x2, [int(p) for p in self.buf.ptrs], self.index, self.full, self.scratch, y, self.N,
                              self.rows_per_shard, native.status_tensor(x.device))
         return y.view(*x.shape[:-1], self.N)
-
-
-# --------------------------------------------------------------------------------------------------
-# F3: expert-parallel dispatch / combine over peer memory
-# --------------------------------------------------------------------------------------------------
-class FusedExpertExchange:
-    """Symmetric buffers and epochs of one expert-parallel group for the fused dispatch and combine kernels.
-
-    ``dispatch(x, idx, counts)`` scatters token rows into the expert owners' receive regions with peer stores
-    (permutation + all-to-all in one pass) and returns the owner-side view: the local receive buffer, its group
-    table and the flat count vector, valid once the kernel that waits for all sources has run on the stream.
-    ``combine(out_rows, pos, weights)`` publishes the local expert outputs and gathers each token's ``k`` outputs
-    from their owners with peer loads while applying the router weights.
-    """
-
-    def __init__(self, ranks: list, group, tokens: int, dim: int, experts: int, k: int, timeout_s: float = 30.0,
-                 num_ctas: int = 128) -> None:
-        from ..ops.moe import row_capacity
-        self.ranks, self.group = list(ranks), group
-        self.ep = len(ranks)
-        self.me = self.ranks.index(dist.get_rank()) if self.ep > 1 else 0
-        self.T, self.D, self.E, self.k = tokens, dim, experts, k
-        self.El = experts // self.ep
-        self.cap = row_capacity(tokens, k, self.El)
-        self.timeout_s, self.num_ctas = timeout_s, num_ctas
-        rows = self.ep * self.cap
-        self.recv = SymmetricBuffer.create(rows * dim * 2, self.ranks, group)
-        self.out = SymmetricBuffer.create(rows * dim * 2, self.ranks, group)
-        self.meta = SymmetricBuffer.create(self.ep * self.El * 4, self.ranks, group)
-        self.flags = SymmetricBuffer.create(2 * self.ep * 8, self.ranks, group)
-        dev = self.recv.local.device
-        self.recv_rows = self.recv.view(torch.bfloat16, rows * dim).view(rows, dim)
-        self.out_rows = self.out.view(torch.bfloat16, rows * dim).view(rows, dim)
-        self.meta_local = self.meta.view(torch.int32, self.ep * self.El)
-        self.flags_local = self.flags.view(torch.int64, 2 * self.ep)
-        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.epoch = 0
-        torch.cuda.synchronize()
-        if self.ep > 1:
-            dist.barrier(group=group)
-
-    def dispatch(self, x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor):
-        lib = native.lib()
-        dev = x.device
-        self.epoch += 1
-        seg_off = torch.empty(self.E, dtype=torch.int32, device=dev)
-        cursor = torch.zeros(self.E, dtype=torch.int32, device=dev)
-        pos = torch.empty(x.shape[0] * self.k, dtype=torch.int32, device=dev)
-        lib.ep_dispatch_push(x.contiguous(), idx, counts, seg_off, cursor, pos, self.recv.peer_ptrs, self.meta.peer_ptrs,
-                             self.flags.peer_ptrs, self.counter, self.me, self.ep, self.cap, self.epoch, self.num_ctas)
-        G = self.ep * self.El
-        g_start = torch.empty(G, dtype=torch.int32, device=dev)
-        g_len = torch.empty(G, dtype=torch.int32, device=dev)
-        recv_counts = torch.empty(G, dtype=torch.int32, device=dev)
-        lib.ep_wait_table(self.flags_local, self.meta_local, g_start, g_len, recv_counts, self.ep, self.cap, self.epoch,
-                          self.timeout_s, native.status_tensor(dev))
-        return self.recv_rows, pos, g_start, g_len, recv_counts
-
-    def combine(self, pos: torch.Tensor, weights: torch.Tensor, tokens: int) -> torch.Tensor:
-        """Call after the expert outputs of this epoch have been written to ``self.out_rows``."""
-        lib = native.lib()
-        dev = weights.device
-        lib.ep_signal(self.flags.peer_ptrs, self.ep, self.me, self.ep, self.epoch)
-        out = torch.empty((tokens, self.D), dtype=torch.bfloat16, device=dev)
-        lib.ep_combine_pull(self.out.peer_ptrs, pos, weights.contiguous(), out, self.flags_local[self.ep:], self.ep,
-                            self.cap, self.epoch, self.timeout_s, native.status_tensor(dev), self.num_ctas)
-        return out

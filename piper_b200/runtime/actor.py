@@ -234,6 +234,16 @@ class PiperActor:
             n = self.dag.nodes[uid]
             if n.node_kind == REDUCE:
                 n.node_meta["noop"] = last[n.node_meta.get("bucket_key")] != uid
+        # the last reduce-scatter of a bucket in a step is where the fused lowering applies the optimizer
+        last_rs: dict[str, str] = {}
+        for uid in self.order:
+            n = self.dag.nodes[uid]
+            if n.node_kind == REDUCE_SCATTER:
+                last_rs[n.node_meta.get("bucket_key")] = uid
+        for uid in self.order:
+            n = self.dag.nodes[uid]
+            if n.node_kind == REDUCE_SCATTER:
+                n.node_meta["last_sync"] = last_rs[n.node_meta.get("bucket_key")] == uid
 
     # -------------------------------------------------------------- data
     def load_input(self, inputs: list) -> None:
@@ -555,7 +565,7 @@ class DagExecutor:
         self.shape_ref[node.uid] = [(tuple(o.shape), o.dtype) for o in outs
                                     if isinstance(o, torch.Tensor) and o.is_floating_point()]
         if node.node_meta.get("zero_free_full_params_after") and bucket.storage is not None:
-            bucket.storage.free_params(a.streams.get(node.stream) if self.cuda else None)
+            self._free_params(bucket.storage, node)
 
     def _output_grads(self, node: TrainingDAGNode):
         """Gradients w.r.t. this segment's outputs from the downstream backward / receive / exchange node.
@@ -626,7 +636,7 @@ class DagExecutor:
         if st is not None and st.flat_grads is not None:
             st.absorb_autograd_grads()
         if not split and node.node_meta.get("zero_free_full_params_after") and st is not None:
-            st.free_params(a.streams.get(node.stream) if self.cuda else None)
+            self._free_params(st, node)
         if a.ep_fused is not None:
             a.ep_fused.after_node(node)
 
@@ -650,7 +660,7 @@ class DagExecutor:
         if st is not None and st.flat_grads is not None:
             st.absorb_autograd_grads()
         if node.node_meta.get("zero_free_full_params_after") and st is not None:
-            st.free_params(a.streams.get(node.stream) if self.cuda else None)
+            self._free_params(st, node)
         if a.ep_fused is not None:
             a.ep_fused.after_node(node)
 
@@ -713,8 +723,7 @@ class DagExecutor:
             return
         a = self.a
         if a.fused is not None and a.fused.supports(st):
-            a.fused.reduce_scatter_adam(st, 1.0 / (a.num_microbatches * a.layout.dp_degree))
-            st.fused_stepped = True
+            a.fused.reduce(st, True, 1.0 / (a.num_microbatches * a.layout.dp_degree))
         else:
             st.all_reduce_grads(per_tensor=(a.baseline == "nccl"))
 
@@ -724,7 +733,13 @@ class DagExecutor:
             return
         if not st.release_grads():
             if node.node_meta.get("zero_free_full_params_after"):
-                st.free_params(self.a.streams.get(node.stream) if self.cuda else None)
+                self._free_params(st, node)
+            return
+        a = self.a
+        if a.fused is not None and a.fused.supports(st):
+            a.fused.reduce(st, bool(node.node_meta.get("last_sync")), 1.0 / (a.num_microbatches * a.layout.dp_degree))
+            if node.node_meta.get("zero_free_full_params_after"):
+                self._free_params(st, node)
             return
         st.reduce_scatter_grads()
         if st.mode == "zero3":
@@ -736,8 +751,21 @@ class DagExecutor:
 
     def _all_gather(self, node: TrainingDAGNode) -> None:
         st = self._storage_of(node)
-        if st is not None and st.mode == "zero3":
+        if st is None or st.mode != "zero3":
+            return
+        a = self.a
+        if a.fused is not None and a.fused.supports(st):
+            consumer = self.dag.nodes.get(node.node_meta.get("compute_uid"))
+            fwd = consumer is not None and consumer.node_kind == COMPUTE and consumer.compute_subkind == "FWD" \
+                and not a.activation_checkpointing
+            a.fused.gather(st, fuse_first=fwd)
+        else:
             st.all_gather_params()
+
+    def _free_params(self, st: ParamStorage, node: TrainingDAGNode) -> None:
+        if self.a.fused is not None and self.a.fused.supports(st) and st.param_users <= 1:
+            self.a.fused.release(st)
+        st.free_params(self.a.streams.get(node.stream) if self.cuda else None)
 
     def _all_to_all(self, node: TrainingDAGNode) -> None:
         from ..parallel.expert import exchange_tokens

@@ -31,14 +31,11 @@ def _rank_state(actor) -> dict:
         if st is None or st.numel == 0:
             continue
         flat = st.full_param_tensor()
-        lo, hi = st.owned_range() if not hasattr(st, "fused_shard") else st.fused_shard
         for s in st.slots:
+            model[s.fqn] = flat[s.offset:s.offset + s.numel].view(s.shape).detach().cpu().clone()
+        for s, a, e, sh in st.owned_pieces():
             key = s.fqn
-            model[key] = flat[s.offset:s.offset + s.numel].view(s.shape).detach().cpu().clone()
-            a, e = max(s.offset, lo), min(s.offset + s.numel, hi)
-            if a >= e:
-                continue
-            sl = slice(a - lo, e - lo)
+            sl = slice(sh, sh + e - a)
             entry = {"step": st.step_count, "exp_avg": st.m[sl].cpu().clone(), "exp_avg_sq": st.v[sl].cpu().clone()}
             if getattr(st, "master", None) is not None:
                 entry["master"] = st.master[sl].cpu().clone()
@@ -131,7 +128,7 @@ def load_checkpoint(actor, directory: str) -> int:
         st = b.storage
         if st is None or st.numel == 0:
             continue
-        lo, hi = st.owned_range() if not hasattr(st, "fused_shard") else st.fused_shard
+        pieces = {id(s): (a, z, sh) for s, a, z, sh in st.owned_pieces()}
         was_live = st.params_live
         if not was_live:
             st.all_gather_params()
@@ -147,11 +144,11 @@ def load_checkpoint(actor, directory: str) -> int:
                 if e is not None:
                     e = {k: (v[sel] if isinstance(v, torch.Tensor) else v) for k, v in e.items()}
             st.flat_params[s.offset:s.offset + s.numel].copy_(t.reshape(-1).to(st.dtype))
-            a, z = max(s.offset, lo), min(s.offset + s.numel, hi)
-            if a < z:
-                own = slice(a - lo, z - lo)
+            if id(s) in pieces:
+                a, z, sh = pieces[id(s)]
+                own = slice(sh, sh + z - a)
                 src = slice(a - s.offset, z - s.offset)
-                if st.params_sharded or st.sharded_state or hasattr(st, "fused_shard"):
+                if st.params_sharded or st.sharded_state or st.row_table is not None:
                     st.shard_params[own].copy_(t.reshape(-1)[src].to(st.dtype))
                 if e is not None:
                     st.m[own].copy_(e["exp_avg"].reshape(-1)[src])

@@ -82,6 +82,7 @@ class AdamConfig:
     betas: tuple = (0.9, 0.999)
     eps: float = 1e-8
     weight_decay: float = 0.0
+    decoupled: bool = False     # True: AdamW (decay shrinks the weight); False: torch.optim.Adam's L2 term in the gradient
 
 
 class ParamStorage:
@@ -116,6 +117,11 @@ class ParamStorage:
         self.params_live = False
         self.param_users = 0
         self.grad_users = 0
+        # row sharding (the fused data-parallel paths): per slot (offset of this rank's piece in the shard buffers,
+        # elements per piece); None = the shard is the contiguous range owned_range() of the flat layout
+        self.row_table: Optional[list] = None
+        self.persistent_grads = False      # the full gradient buffer is never freed (it lives in symmetric memory)
+        self.fused_stepped = False
         if self.numel == 0:
             return
         full = torch.zeros(self.numel, dtype=dtype, device=device)
@@ -153,6 +159,59 @@ class ParamStorage:
         if self.mode in ("zero2", "zero3"):
             return self.dp_rank * self.shard_numel, (self.dp_rank + 1) * self.shard_numel
         return 0, self.numel
+
+    def owned_pieces(self) -> list:
+        """``(slot, a, e, sh)``: this rank keeps optimizer state (and, when parameters are sharded, the
+        parameters) of elements ``[a, e)`` of the flat layout at ``[sh, sh + e - a)`` of its shard buffers."""
+        out = []
+        if self.row_table is not None:
+            for s, (sh, stride) in zip(self.slots, self.row_table):
+                a = s.offset + self.dp_rank * stride
+                e = min(s.offset + s.numel, a + stride)
+                if a < e:
+                    out.append((s, a, e, sh))
+            return out
+        lo, hi = self.owned_range()
+        for s in self.slots:
+            a, e = max(s.offset, lo), min(s.offset + s.numel, hi)
+            if a < e:
+                out.append((s, a, e, a - lo))
+        return out
+
+    @staticmethod
+    def row_layout(slots: list, dp: int) -> tuple[list, int]:
+        """Row sharding of a bucket: parameter ``[N, K]`` is cut into ``dp`` pieces of ``R = ceil(N / dp)`` rows
+        rounded up to 64; returns ([(offset of the piece in a shard, elements per piece)], shard length)."""
+        table, sh = [], 0
+        for s in slots:
+            n_rows = int(s.shape[0]) if len(s.shape) >= 1 else 1
+            k = 1
+            for d in s.shape[1:]:
+                k *= int(d)
+            rows = ((n_rows + dp - 1) // dp + 63) // 64 * 64
+            table.append((sh, rows * k))
+            sh += rows * k
+        return table, sh
+
+    def convert_to_rows(self, alloc: Callable) -> None:
+        """Re-shard the optimizer state (and parameter shard) of this bucket by parameter rows.
+
+        ``alloc(name, numel, dtype)`` returns the zeroed buffer for ``shard_params`` / ``shard_grads`` (the fused
+        paths pass symmetric memory).  Must run before training or right after a checkpoint was loaded into the
+        full parameters: master weights are re-derived from the current parameters, moments restart at zero.
+        """
+        full = self.full_param_tensor()
+        table, shard = self.row_layout(self.slots, self.dp_degree)
+        self.row_table = table
+        self.shard_numel = shard
+        self.master = torch.zeros(shard, dtype=torch.float32, device=self.device)
+        self.m = torch.zeros(shard, dtype=torch.float32, device=self.device)
+        self.v = torch.zeros(shard, dtype=torch.float32, device=self.device)
+        self.shard_params = alloc("shard_params", shard, self.dtype)
+        self.shard_grads = alloc("shard_grads", shard, torch.float32)
+        for s, a, e, sh in self.owned_pieces():
+            self.master[sh:sh + e - a].copy_(full[a:e].to(torch.float32))
+            self.shard_params[sh:sh + e - a].copy_(full[a:e])
 
     def _bind(self, flat: torch.Tensor) -> None:
         """Create the parameter tensors once: leaves over ``flat``'s storage with their own version counters,
@@ -234,7 +293,7 @@ class ParamStorage:
         return self.grad_users == 0
 
     def free_grads(self, consumer_stream=None) -> None:
-        if self.numel == 0 or not self.params_sharded or self.flat_grads is None:
+        if self.numel == 0 or not self.params_sharded or self.flat_grads is None or self.persistent_grads:
             return
         for p in self.param_views.values():
             ops_core.grad_sinks.unregister(p)
@@ -281,6 +340,8 @@ class ParamStorage:
     def step(self, grad_scale: float) -> None:
         if self.numel == 0:
             return
+        if self.row_table is not None:
+            raise RuntimeError(f"bucket {self.key}: a row-sharded bucket is stepped by the fused reduction kernel")
         self.step_count += 1
         lo, hi = self.owned_range()
         grads = self.shard_grads if self.sharded_state else self.flat_grads[lo:hi]
@@ -288,7 +349,7 @@ class ParamStorage:
         a = self.adam
         if grads.is_cuda and self.dtype == torch.bfloat16:
             native.lib().adam_flat(self.master, self.m, self.v, grads, target, a.lr, a.betas[0], a.betas[1], a.eps,
-                                   a.weight_decay, self.step_count, grad_scale)
+                                   a.weight_decay, self.step_count, grad_scale, a.decoupled)
         else:
             _adam_reference(self.master if self.master is not None else target, self.m, self.v, grads,
                             target if self.master is not None else None, a, self.step_count, grad_scale)
@@ -305,12 +366,9 @@ class ParamStorage:
         """fqn -> scaled copy of the gradient this rank holds (full tensors, or its ZeRO shard as a flat range)."""
         out = {}
         if self.sharded_state:
-            lo, hi = self.owned_range()
             g = self.shard_grads * scale
-            for s in self.slots:
-                a, b = max(s.offset, lo), min(s.offset + s.numel, hi)
-                if a < b:
-                    out[s.fqn] = (a - s.offset, g[a - lo:b - lo].clone())
+            for s, a, e, sh in self.owned_pieces():
+                out[s.fqn] = (a - s.offset, g[sh:sh + e - a].clone())
         elif self.flat_grads is not None:
             for s in self.slots:
                 out[s.fqn] = (self.flat_grads[s.offset:s.offset + s.numel] * scale).view(s.shape).clone()
@@ -321,6 +379,14 @@ class ParamStorage:
         if self.params_live:
             return self.flat_params
         flat = torch.empty(self.numel, dtype=self.dtype, device=self.device)
+        if self.row_table is not None:
+            # row-sharded: every rank contributes its pieces
+            mine = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            for _s, a, e, sh in self.owned_pieces():
+                mine[a:e].copy_(self.shard_params[sh:sh + e - a])
+            if self.dp_degree > 1:
+                dist.all_reduce(mine, group=self.dp_group)
+            return mine
         if self.dp_degree > 1:
             dist.all_gather_into_tensor(flat, self.shard_params, group=self.dp_group)
         else:
@@ -333,13 +399,16 @@ def _adam_reference(master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad
     """The math of the flat Adam kernel in PyTorch ops (CPU runs and fp32 parameters)."""
     with torch.no_grad():
         g = grad * grad_scale
+        if a.weight_decay and not a.decoupled:
+            g = g + a.weight_decay * master
         m.mul_(a.betas[0]).add_(g, alpha=1 - a.betas[0])
         v.mul_(a.betas[1]).addcmul_(g, g, value=1 - a.betas[1])
         bc1 = 1 - a.betas[0] ** step
         bc2 = 1 - a.betas[1] ** step
         denom = (v / bc2).sqrt_().add_(a.eps)
-        if a.weight_decay:
-            master.mul_(1 - a.lr * a.weight_decay)
-        master.addcdiv_(m / bc1, denom, value=-a.lr)
+        upd = (m / bc1) / denom
+        if a.weight_decay and a.decoupled:
+            upd = upd + a.weight_decay * master
+        master.add_(upd, alpha=-a.lr)
         if param_out is not None:
             param_out.copy_(master)

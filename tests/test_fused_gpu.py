@@ -7,34 +7,140 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_f1_peer_wait_times_out_cleanly():
-    """A peer flag that nothing sets: the kernel gives up after the deadline, reports status 2, context stays usable."""
+def test_peer_wait_times_out_cleanly():
+    """A peer flag that nothing sets: the wait kernel gives up after the deadline, reports status 2 with the tag of
+    the wait, the reduction kernel behind it does nothing, and the context stays usable."""
     from piper_b200.ops import native
 
     lib = native.lib()
     dev = torch.device("cuda")
+    flags = torch.zeros(6, device=dev, dtype=torch.int64)
+    abort = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = native.status_tensor()
+    status.zero_()
+    lib.ep_wait(flags, 0, 2, 1, 0.2, status, 11, abort)          # waits for two peers to reach use 1
     n = 4096
     grads = [torch.ones(n, device=dev), torch.ones(n, device=dev)]
-    params = [torch.zeros(n, device=dev, dtype=torch.bfloat16) for _ in range(2)]
-    flags = [torch.zeros(4, device=dev, dtype=torch.int64) for _ in range(2)]
     ptr = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
     master = torch.zeros(n // 2, device=dev)
     m, v = torch.zeros_like(master), torch.zeros_like(master)
+    shard = torch.zeros(n // 2, device=dev, dtype=torch.bfloat16)
+    table = torch.tensor([[0], [0], [n // 2], [n]], dtype=torch.int64, device=dev)
     counter = torch.zeros(1, dtype=torch.int32, device=dev)
-    status = native.status_tensor()
-    status.zero_()
-    lib.f1_rs_adam_ag(ptr(grads), ptr(params), ptr(flags), master, m, v, 0, 2, 1, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1,
-                      1.0, counter, status, 0.2, 8)
+    lib.zero_reduce(ptr(grads), None, master, m, v, shard, None, table, 0, 2, False, True, 1e-3, 0.9, 0.999, 1e-8,
+                    0.0, False, 1, 1.0, ptr([flags, flags]), 2, 1, counter, abort, 8)
     torch.cuda.synchronize()
-    with pytest.raises(native.PiperCommTimeout):
+    assert int(abort.item()) == 1
+    with pytest.raises(native.PiperCommTimeout) as err:
         native.check_status()
+    assert "[11," in str(err.value)
     assert int(status.item()) == 0          # reset by check_status
     assert torch.equal(master, torch.zeros_like(master))   # nothing was updated
     x = torch.ones(8, device=dev) * 2       # the context still works
     assert float(x.sum()) == 16.0
 
 
-def _dp_worker(rank, world, fused, steps):
+@pytest.mark.parametrize("dp", [2, 4, 3])
+def test_zero_reduce_and_gather_kernels_with_emulated_ranks(dp):
+    """The reduce-scatter + Adam kernel and the gather kernel, one launch per emulated rank with every rank's
+    buffers in this GPU's memory (no launch waits for another), against the plain formulas."""
+    from piper_b200.ops import native
+    from piper_b200.runtime.storage import ALIGN, ParamSlot, ParamStorage
+
+    lib = native.lib()
+    dev = torch.device("cuda")
+    torch.manual_seed(dp)
+    shapes = [(300, 64), (130,), (64, 128), (1000, 8)]
+    slots, off = [], 0
+    for i, sh in enumerate(shapes):
+        n = 1
+        for d in sh:
+            n *= d
+        slots.append(ParamSlot(pos=i, fqn=f"p{i}", shape=sh, dtype=torch.bfloat16, requires_grad=True, offset=off, numel=n))
+        off += (n + ALIGN - 1) // ALIGN * ALIGN
+    numel = (off + ALIGN * dp - 1) // (ALIGN * dp) * (ALIGN * dp)
+    table_py, S = ParamStorage.row_layout(slots, dp)
+    table = torch.tensor([[s.offset for s in slots], [t[0] for t in table_py], [t[1] for t in table_py],
+                          [(s.numel + 63) // 64 * 64 for s in slots]], dtype=torch.int64, device=dev)
+    ptr = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+    valid = torch.zeros(numel, dtype=torch.bool, device=dev)
+    for s in slots:
+        valid[s.offset:s.offset + s.numel] = True
+    params0 = (torch.randn(numel, device=dev) * 0.1 * valid).to(torch.bfloat16)
+    grads = [torch.randn(numel, device=dev) * valid for _ in range(dp)]
+    grads2 = [torch.randn(numel, device=dev) * valid for _ in range(dp)]
+    gsum = sum(grads) + sum(grads2)
+    full_grads = [g.clone() for g in grads]
+    full_params = [params0.clone() for _ in range(dp)]
+    flags = [torch.zeros(3 * dp, dtype=torch.int64, device=dev) for _ in range(dp)]
+    abort = torch.zeros(1, dtype=torch.int32, device=dev)
+    st = {}
+
+    def pieces(r):
+        for s, (sh, stride) in zip(slots, table_py):
+            a = s.offset + r * stride
+            e = min(s.offset + s.numel, a + stride)
+            if a < e:
+                yield a, e, sh
+
+    for r in range(dp):
+        master = torch.zeros(S, device=dev)
+        shard_p = torch.zeros(S, device=dev, dtype=torch.bfloat16)
+        for a, e, sh in pieces(r):
+            master[sh:sh + e - a] = params0[a:e].float()
+            shard_p[sh:sh + e - a] = params0[a:e]
+        st[r] = dict(master=master, m=torch.zeros(S, device=dev), v=torch.zeros(S, device=dev), shard_p=shard_p,
+                     shard_g=torch.zeros(S, device=dev), counter=torch.zeros(1, dtype=torch.int32, device=dev))
+    lr, b1, b2, eps, wd, scale = 1e-2, 0.9, 0.95, 1e-8, 0.1, 0.25
+
+    def launch(r, final):
+        d = st[r]
+        lib.zero_reduce(ptr(full_grads), d["shard_g"], d["master"], d["m"], d["v"], d["shard_p"],
+                        ptr(full_params) if final else None, table, r, dp, True, final, lr, b1, b2, eps, wd, True, 1,
+                        scale, ptr(flags), dp, 1 + int(final), d["counter"], abort, 16)
+
+    for r in range(dp):                       # first gradient chain: accumulate only
+        launch(r, False)
+    torch.cuda.synchronize()
+    for r in range(dp):
+        for a, e, sh in pieces(r):
+            want = sum(g[a:e] for g in grads)
+            assert torch.allclose(st[r]["shard_g"][sh:sh + e - a], want, atol=1e-5)
+            assert torch.count_nonzero(full_grads[r][a:e]) == 0          # own piece cleared
+    for r in range(dp):                       # second chain: new gradients everywhere, then the final reduction
+        full_grads[r].copy_(grads2[r])
+    for r in range(dp):
+        launch(r, True)
+    torch.cuda.synchronize()
+    native.check_status()
+    g = gsum * scale
+    m_ref = (1 - b1) * g
+    v_ref = (1 - b2) * g * g
+    w0 = params0.float()
+    w_ref = w0 - lr * (m_ref / (1 - b1)) / ((v_ref / (1 - b2)).sqrt() + eps) - lr * wd * w0
+    for r in range(dp):
+        assert all(int(f[dp + r]) == 2 for f in flags)                   # DONE published to every rank
+        for a, e, sh in pieces(r):
+            assert torch.allclose(st[r]["master"][sh:sh + e - a], w_ref[a:e], atol=1e-5, rtol=1e-5)
+            assert torch.count_nonzero(st[r]["shard_g"][sh:sh + e - a]) == 0
+            for q in range(dp):                                            # update stored into every rank's buffer
+                assert torch.equal(full_params[q][a:e], w_ref[a:e].to(torch.bfloat16))
+    # gather: every rank's shard back into a full buffer, with and without a skipped parameter
+    shards = [st[r]["shard_p"] for r in range(dp)]
+    full = torch.zeros(numel, device=dev, dtype=torch.bfloat16)
+    lib.zero_gather(ptr(shards), full, table, dp, -1, None, 16)
+    torch.cuda.synchronize()
+    for s in slots:
+        assert torch.equal(full[s.offset:s.offset + s.numel], w_ref[s.offset:s.offset + s.numel].to(torch.bfloat16))
+    full.zero_()
+    lib.zero_gather(ptr(shards), full, table, dp, 0, None, 16)
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(full[:slots[0].numel]) == 0
+    s = slots[2]
+    assert torch.equal(full[s.offset:s.offset + s.numel], w_ref[s.offset:s.offset + s.numel].to(torch.bfloat16))
+
+
+def _dp_worker(rank, world, fused, steps, mode="allreduce"):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     os.environ["PIPER_FUSED"] = "1" if fused else "0"
     import torch
@@ -52,8 +158,14 @@ def _dp_worker(rank, world, fused, steps):
     per = 8 // world
     xs, ys = x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per]
     devs = list(range(world))
-    sched = [{"op": "place", "filter": {"PP": 0}, "devices": devs},
-             {"op": "replicate", "filter": {"PP": 0}, "devices": devs, "reduce_stream": "dp_stream"},
+    rep = {"op": "replicate", "filter": {"PP": 0}, "devices": devs, "reduce_stream": "dp_stream"}
+    if mode == "zero2":
+        rep.update({"shard_grads": True, "bucket_size": 1})
+    elif mode == "zero3":
+        rep.update({"shard_params": True, "gather_stream": "gather_stream", "bucket_size": 1})
+    elif mode == "bucketed":
+        rep.update({"bucket_size": 1})
+    sched = [{"op": "place", "filter": {"PP": 0}, "devices": devs}, rep,
              {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 2}]
     actor = piper_setup(Transformer, (cfg, seq, 1), optim_fn=torch.optim.Adam, optim_kwargs={"lr": 1e-3},
                         example_inputs=[xs], example_outputs=ys, model_dtype=torch.bfloat16,
@@ -65,26 +177,41 @@ def _dp_worker(rank, world, fused, steps):
     torch.cuda.synchronize()
     native.check_status()
     params = {k: v.float().cpu() for k, v in actor.named_parameters().items()}
-    return {"losses": losses, "params": params}
+    return {"losses": losses, "params": params, "buckets": len(actor.buckets),
+            "gather_gemms": sum(1 for b in (actor.fused.buckets.values() if actor.fused else ()) if b.first_slot >= 0)}
+
+
+def _dp_modes_worker(rank, world, modes, steps):
+    """Every data-parallel mode with the fused and with the NCCL lowering, in one set of processes."""
+    out = {}
+    for mode in modes:
+        for fused in (True, False):
+            out[(mode, fused)] = _dp_worker(rank, world, fused, steps, mode)
+    return out
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_f1_matches_nccl_allreduce_adam_on_two_gpus(tmp_path):
+def test_fused_data_parallel_paths_match_the_nccl_lowering_on_two_gpus(tmp_path):
     from tests.dist_utils import run_ranks
 
-    (tmp_path / "a").mkdir()
-    (tmp_path / "b").mkdir()
-    fused = run_ranks(2, _dp_worker, (True, 4), tmp_path / "a", timeout=600)
-    base = run_ranks(2, _dp_worker, (False, 4), tmp_path / "b", timeout=600)
-    # replicas agree with each other bit-for-bit after the fused all-gather
-    for k in fused[0]["params"]:
-        assert torch.equal(fused[0]["params"][k], fused[1]["params"][k]), k
-    # and with the NCCL lowering up to reduction order and bf16 rounding
-    for k, p in fused[0]["params"].items():
-        d = (p - base[0]["params"][k]).abs()
-        assert d.max() <= 8e-3 and d.mean() < 2e-4, (k, float(d.max()), float(d.mean()))
-    assert abs(fused[0]["losses"][-1][0] - base[0]["losses"][-1][0]) < 5e-2
-    assert fused[0]["losses"][-1][0] < fused[0]["losses"][0][0]
+    modes = ["allreduce", "bucketed", "zero2", "zero3"]
+    res = run_ranks(2, _dp_modes_worker, (modes, 4), tmp_path, timeout=900)
+    for mode in modes:
+        fused = [r[(mode, True)] for r in res]
+        base = [r[(mode, False)] for r in res]
+        if mode != "allreduce":
+            assert fused[0]["buckets"] > 1, mode
+        if mode == "zero3":
+            assert fused[0]["gather_gemms"] >= 1        # some bucket gathers its first weight inside the GEMM
+        # replicas agree with each other bit-for-bit after the fused update
+        for k in fused[0]["params"]:
+            assert torch.equal(fused[0]["params"][k], fused[1]["params"][k]), (mode, k)
+        # and with the NCCL lowering up to reduction order and bf16 rounding
+        for k, p in fused[0]["params"].items():
+            d = (p - base[0]["params"][k]).abs()
+            assert d.max() <= 8e-3 and d.mean() < 2e-4, (mode, k, float(d.max()), float(d.mean()))
+        assert abs(fused[0]["losses"][-1][0] - base[0]["losses"][-1][0]) < 5e-2, mode
+        assert fused[0]["losses"][-1][0] < fused[0]["losses"][0][0], mode
 
 
 def _f2_worker(rank, world):
@@ -226,6 +353,10 @@ def _moe_run(rank, world, fused, steps, schedule="plain"):
     return {"losses": losses, "params": params, "grads": grads, "slots": slots}
 
 
+def _moe_both(rank, world, steps):
+    return _moe_run(rank, world, True, steps), _moe_run(rank, world, False, steps)
+
+
 def _check_moe_pair(fused, base):
     assert fused["slots"] >= 1
     for a, b in zip(fused["losses"], base["losses"]):
@@ -257,12 +388,9 @@ def test_fused_expert_exchange_matches_the_local_lowering_on_one_gpu(schedule):
 def test_fused_expert_exchange_matches_all_to_all_on_two_gpus(tmp_path):
     from tests.dist_utils import run_ranks
 
-    (tmp_path / "a").mkdir()
-    (tmp_path / "b").mkdir()
-    fused = run_ranks(2, _moe_run, (True, 4), tmp_path / "a", timeout=600)
-    base = run_ranks(2, _moe_run, (False, 4), tmp_path / "b", timeout=600)
+    res = run_ranks(2, _moe_both, (4,), tmp_path, timeout=900)
     for r in range(2):
-        _check_moe_pair(fused[r], base[r])
+        _check_moe_pair(res[r][0], res[r][1])
 
 
 def test_expert_dispatch_rejects_a_region_overflow():

@@ -240,7 +240,7 @@ def test_swiglu_embedding_ce_adam():
     pr = master.clone().requires_grad_(True)
     opt = torch.optim.Adam([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
     for step in (1, 2):
-        native.lib().adam_flat(master, m, v, grad, p16, 1e-2, 0.9, 0.95, 1e-8, 0.0, step, 1.0)
+        native.lib().adam_flat(master, m, v, grad, p16, 1e-2, 0.9, 0.95, 1e-8, 0.0, step, 1.0, True)
         pr.grad = grad.clone()
         opt.step()
     assert _rel_err(master, pr.detach()) < 1e-5

@@ -272,3 +272,65 @@ def test_status_monitor_raises_for_the_previous_step_with_a_fake_status_word():
     with pytest.raises(native.PiperKernelError):
         mon.poll(wait=True)
     mon.poll()                      # nothing pending any more
+
+
+def test_row_sharding_partitions_every_parameter_and_rebuilds_it():
+    """Row sharding of a bucket (used by the fused data-parallel paths): the ranks' pieces tile every parameter
+    exactly once, shard buffers hold the pieces, and decay follows torch.optim.Adam vs AdamW."""
+    import torch
+
+    from piper_b200.runtime.storage import AdamConfig, ParamSlot, ParamStorage, _adam_reference
+
+    shapes = {"a.weight": (300, 16), "norm.weight": (130,), "b.weight": (64, 24)}
+    dp = 3
+    stores = []
+    for r in range(dp):
+        slots = [ParamSlot(pos=i, fqn=k, shape=v, dtype=torch.float32, requires_grad=True)
+                 for i, (k, v) in enumerate(shapes.items())]
+        st = ParamStorage("bucket", slots, torch.device("cpu"), torch.float32, "zero2", r, dp, None, AdamConfig())
+        st.convert_to_rows(lambda name, n, dt: torch.zeros(n, dtype=dt))
+        stores.append(st)
+    full = stores[0].flat_params
+    covered = torch.zeros(stores[0].numel, dtype=torch.int32)
+    rebuilt = torch.zeros_like(full)
+    for st in stores:
+        assert st.shard_numel == stores[0].shard_numel
+        for s, a, e, sh in st.owned_pieces():
+            covered[a:e] += 1
+            rebuilt[a:e] = st.shard_params[sh:sh + e - a]
+            assert torch.equal(st.master[sh:sh + e - a], full[a:e].float())
+            k = s.numel // s.shape[0]
+            assert (a - s.offset) % k == 0                     # pieces start on a row boundary
+    for s in stores[0].slots:
+        assert torch.all(covered[s.offset:s.offset + s.numel] == 1)
+        assert torch.equal(rebuilt[s.offset:s.offset + s.numel], full[s.offset:s.offset + s.numel])
+
+    # decay semantics of the flat optimizer against torch.optim
+    for cls, decoupled in ((torch.optim.Adam, False), (torch.optim.AdamW, True)):
+        w = torch.nn.Parameter(torch.randn(50))
+        opt = cls([w], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+        master, m, v = w.detach().clone(), torch.zeros(50), torch.zeros(50)
+        cfg = AdamConfig(lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, decoupled=decoupled)
+        for step in range(1, 4):
+            g = torch.randn(50)
+            w.grad = g.clone()
+            opt.step()
+            _adam_reference(master, m, v, g, None, cfg, step, 1.0)
+            assert torch.allclose(master, w.detach(), atol=1e-6), cls
+
+
+def test_optimizer_mapping_rejects_what_the_kernels_cannot_do():
+    import functools
+
+    import pytest
+    import torch
+
+    from piper_b200.engine import _adam_config
+
+    assert _adam_config(torch.optim.Adam, {"lr": 3e-4, "weight_decay": 0.1}).decoupled is False
+    cfg = _adam_config(functools.partial(torch.optim.AdamW, lr=1e-3, fused=True), None)
+    assert cfg.decoupled is True and cfg.weight_decay == 1e-2 and cfg.lr == 1e-3
+    with pytest.raises(ValueError):
+        _adam_config(torch.optim.SGD, {"lr": 0.1})
+    with pytest.raises(ValueError):
+        _adam_config(torch.optim.Adam, {"amsgrad": True})

@@ -364,7 +364,7 @@ class FusedExpertRuntime:
             lib.ep_block_push(rows, g_start, g_len, p.meta[ex.slot][G:2 * G], p.El, 0, p.cap_loc, dst, p.flags_ptrs,
                               p.flags_local, p.off(b, FREE), self._free_needed(b, use), p.off(b, READY), use,
                               p.counters[b:b + 1], p.aborts[b:b + 1], self.me, self.ep, self.timeout_s, status, self.num_ctas)
-            lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 4 if kind == "F_out" else 6)
+            lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 4 if kind == "F_out" else 6, None)
             if kind == "F_out":
                 ex.ret_use = use
                 out[ti] = p.ret[i]
@@ -380,7 +380,7 @@ class FusedExpertRuntime:
                           p.gin_ptrs[i], p.flags_ptrs, p.flags_local, p.off(b, FREE), self._free_needed(b, use),
                           p.off(b, READY), use, p.counters[b:b + 1], p.aborts[b:b + 1], self.me, self.ep,
                           self.timeout_s, status, self.num_ctas)
-        lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 5)
+        lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 5, None)
         ex.gin_use = use
         if ex.split_backward:
             # the deferred weight-gradient GEMMs read these rows long after the ring has moved on

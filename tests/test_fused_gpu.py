@@ -123,21 +123,23 @@ def test_zero_reduce_and_gather_kernels_with_emulated_ranks(dp):
         for a, e, sh in pieces(r):
             assert torch.allclose(st[r]["master"][sh:sh + e - a], w_ref[a:e], atol=1e-5, rtol=1e-5)
             assert torch.count_nonzero(st[r]["shard_g"][sh:sh + e - a]) == 0
+            new16 = st[r]["master"][sh:sh + e - a].to(torch.bfloat16)
+            assert torch.equal(st[r]["shard_p"][sh:sh + e - a], new16)
             for q in range(dp):                                            # update stored into every rank's buffer
-                assert torch.equal(full_params[q][a:e], w_ref[a:e].to(torch.bfloat16))
+                assert torch.equal(full_params[q][a:e], new16)
     # gather: every rank's shard back into a full buffer, with and without a skipped parameter
     shards = [st[r]["shard_p"] for r in range(dp)]
     full = torch.zeros(numel, device=dev, dtype=torch.bfloat16)
     lib.zero_gather(ptr(shards), full, table, dp, -1, None, 16)
     torch.cuda.synchronize()
     for s in slots:
-        assert torch.equal(full[s.offset:s.offset + s.numel], w_ref[s.offset:s.offset + s.numel].to(torch.bfloat16))
+        assert torch.equal(full[s.offset:s.offset + s.numel], full_params[0][s.offset:s.offset + s.numel])
     full.zero_()
     lib.zero_gather(ptr(shards), full, table, dp, 0, None, 16)
     torch.cuda.synchronize()
     assert torch.count_nonzero(full[:slots[0].numel]) == 0
     s = slots[2]
-    assert torch.equal(full[s.offset:s.offset + s.numel], w_ref[s.offset:s.offset + s.numel].to(torch.bfloat16))
+    assert torch.equal(full[s.offset:s.offset + s.numel], full_params[0][s.offset:s.offset + s.numel])
 
 
 def _dp_worker(rank, world, fused, steps, mode="allreduce"):

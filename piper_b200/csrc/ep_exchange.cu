@@ -107,8 +107,10 @@ ep_dispatch_push_kernel(const __nv_bfloat16* __restrict__ x, const int* __restri
       pos_loc[t * k + lane] = p < 0 ? 0 : p;
     }
     const uint4* src = reinterpret_cast<const uint4*>(x + t * D);
-    // the row is read once (four vectors per lane per trip) and stored k times
-    for (int i0 = lane; i0 < vecs; i0 += 128) {
+    // the row is read once (four vectors per lane per trip) and stored k times; every lane makes the same number
+    // of trips, because the shuffles below need the whole warp
+    for (int base = 0; base < vecs; base += 128) {
+      const int i0 = base + lane;
       uint4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u)

@@ -597,6 +597,15 @@ def bucket_matched_fwd_nodes(dag: TrainingDAG, filters: list[dict], bucket_size_
             dag.connect(a, b, "data")
         for a, b in zip(reversed(b_chain), list(reversed(b_chain))[1:]):
             dag.connect(a, b, "data")
+        # pipeline messages were attached to the nodes this chain replaces: a send now leaves from the end of the
+        # forward (backward) chain and a receive feeds its head
+        for other in dag.nodes.values():
+            if other.node_kind in (SEND, RECV):
+                om = other.node_meta
+                if om.get("from_uid") in (f_uid, b_uid):
+                    om["from_uid"] = last_f if om["from_uid"] == f_uid else last_b
+                if om.get("to_uid") in (f_uid, b_uid):
+                    om["to_uid"] = first_f if om["to_uid"] == f_uid else first_b
         # every bucket's backward gates the update
         for e in out_b:
             if e.dep_kind == "temporal" and dag.nodes[e.dst_uid].node_kind == UPD:

@@ -162,14 +162,14 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
 // blockIdx.y = source rank.
 __global__ void __launch_bounds__(kThreads)
 zero_gather_kernel(const __nv_bfloat16* const* __restrict__ peer_shards, __nv_bfloat16* __restrict__ full, ZeroTable t,
-                   int skip_slot, const int* __restrict__ abort) {
+                   int skip_slot, int only_slot, const int* __restrict__ abort) {
   if (abort != nullptr && abort[0] != 0) return;
   const int p = blockIdx.y;
   const __nv_bfloat16* shard = peer_shards[p];
   const long long stride_thr = static_cast<long long>(gridDim.x) * kThreads;
   const long long first = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
   for (int s = 0; s < t.n; ++s) {
-    if (s == skip_slot) continue;
+    if (s == skip_slot || (only_slot >= 0 && s != only_slot)) continue;
     const long long piece = t.stride[s];
     long long len = t.padded[s] - static_cast<long long>(p) * piece;
     len = len < 0 ? 0 : (len > piece ? piece : len);
@@ -212,13 +212,13 @@ int zero_reduce(const ZeroReduceArgs& a, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-int zero_gather(const void* const* peer_shards, void* full, const ZeroTable& t, int dp, int skip_slot,
+int zero_gather(const void* const* peer_shards, void* full, const ZeroTable& t, int dp, int skip_slot, int only_slot,
                 const int* abort, int num_ctas, cudaStream_t st) {
   if (dp < 1 || t.n < 0 || num_ctas < 1) return -1;
   if (t.n == 0) return 0;
   const dim3 grid(num_ctas, dp);
   zero_gather_kernel<<<grid, kThreads, 0, st>>>(reinterpret_cast<const __nv_bfloat16* const*>(peer_shards),
-                                                static_cast<__nv_bfloat16*>(full), t, skip_slot, abort);
+                                                static_cast<__nv_bfloat16*>(full), t, skip_slot, only_slot, abort);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -267,6 +267,15 @@ class FusedExpertRuntime:
         self.active = None
         moe_ops.set_ep_context(None, None)
 
+    def close(self) -> None:
+        """Collective: unmap the peers' buffers everywhere before any rank frees its own."""
+        torch.cuda.synchronize()
+        if self.pool is not None:
+            for b in self.pool.bufs.values():
+                b.close()
+        if self.ep > 1:
+            dist.barrier(group=self.group)
+
     def after_node(self, node) -> None:
         """Hands buffers back once the node that read them last has been enqueued."""
         for action, key in self.after.get(node.uid, ()):

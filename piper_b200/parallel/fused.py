@@ -146,6 +146,14 @@ class FusedCollectives:
     def supports(self, st: ParamStorage) -> bool:
         return st is not None and st.key in self.buckets
 
+    def close(self) -> None:
+        """Collective: unmap the peers' buffers everywhere before any rank frees its own."""
+        torch.cuda.synchronize()
+        for fb in self.buckets.values():
+            for b in fb.bufs.values():
+                b.close()
+        dist.barrier(group=self.actor.groups.dp_group)
+
     # ------------------------------------------------------------------ gradients
     def reduce(self, st: ParamStorage, final: bool, grad_scale: float) -> None:
         """Reduce-scatter the group's gradient buckets into this rank's shard; with ``final`` also the optimizer
@@ -182,16 +190,23 @@ class FusedCollectives:
         if st.numel == 0:
             return
         st.param_users += 1
-        if st.params_live:
-            return
         fb = self.buckets[st.key]
         lib, lay = native.lib(), self.actor.layout
         dp = lay.dp_degree
+        if st.params_live:
+            # another chain shares the buffer; if its first weight is still waiting for the GEMM that gathers it,
+            # this user may run first: fetch that weight now
+            if fb.first_slot >= 0:
+                w = st.param_views[st.slots[fb.first_slot].pos]
+                if ops_core.gather_gemms.pop(w.data_ptr(), None) is not None:
+                    lib.zero_gather(fb.ptrs("shard_params"), st.flat_params, fb.table, dp, -1, fb.first_slot,
+                                    fb.abort[1:2], self.num_ctas)
+            return
         st.flat_params.untyped_storage().resize_(st.numel * st.flat_params.element_size())
         status = native.status_tensor(st.device)
         lib.ep_wait(fb.flags_local, PARAMS_OFF * dp, dp, fb.version, self.timeout_s, status, 13, fb.abort[1:2])
         skip = fb.first_slot if (fuse_first and fb.first_slot >= 0) else -1
-        lib.zero_gather(fb.ptrs("shard_params"), st.flat_params, fb.table, dp, skip, fb.abort[1:2], self.num_ctas)
+        lib.zero_gather(fb.ptrs("shard_params"), st.flat_params, fb.table, dp, skip, -1, fb.abort[1:2], self.num_ctas)
         st.params_live = True
         st._register_sinks()
         if skip >= 0:

@@ -162,6 +162,9 @@ class PiperActor:
                     self.buckets[key] = self._load_bucket(key, node, modes.get(key, "local"))
         self.order = serial_topological_order(dag)
         self._prune_redundant_grad_sync()
+        computes = [u for u in self.order if dag.nodes[u].node_kind == COMPUTE]
+        self._last_compute_uid = computes[-1] if computes else None
+        self._tail_events = None
 
     def _bucket_modes(self, dag: TrainingDAG) -> dict:
         modes: dict[str, str] = {}
@@ -281,6 +284,15 @@ class PiperActor:
                 torch.cuda.nvtx.range_pop()
         self.iteration += 1
         return out
+
+    def comm_tail_ms(self) -> float:
+        """Device time of the last step between the end of its last compute node and the end of the step: the
+        part of gradient synchronisation and optimizer work that no backward kernel was left to hide."""
+        if self._tail_events is None:
+            return 0.0
+        e0, e1 = self._tail_events
+        e1.synchronize()
+        return float(e0.elapsed_time(e1))
 
     # ---------------------------------------------------- memory / profile
     def reset_peak_memory(self) -> None:
@@ -453,6 +465,7 @@ class DagExecutor:
                     s.wait_stream(cur)
             for s in a._channel_streams.values():
                 s.wait_stream(cur)
+        tail0 = None
         for uid in a.order:
             node = self.dag.nodes[uid]
             kind = node.node_kind
@@ -496,6 +509,9 @@ class DagExecutor:
                 elif kind == UPD:
                     self._update(node)
                 self._record(node)
+                if self.cuda and uid == a._last_compute_uid:
+                    tail0 = torch.cuda.Event(enable_timing=True)
+                    tail0.record(self._stream(node))
                 if a.time_nodes:
                     host_ms = (time.perf_counter() - t_node) * 1e3
                     if self.cuda:
@@ -519,6 +535,10 @@ class DagExecutor:
                     cur.wait_stream(s)
             for s in a._channel_streams.values():
                 cur.wait_stream(s)
+            if a._last_compute_uid is not None:
+                tail1 = torch.cuda.Event(enable_timing=True)
+                tail1.record(cur)
+                a._tail_events = (tail0, tail1)
         a.last_losses = self.losses
         host_s = time.perf_counter() - t0
         a.last_host_time_s = host_s
@@ -679,13 +699,16 @@ class DagExecutor:
             raise RuntimeError(f"{node.uid}: nothing to send from {src}")
         peer = a.layout.peer_rank(node.node_meta["peer_pp_rank"])
         group, tag = self._channel(node)
-        for t in vals:
-            if not isinstance(t, torch.Tensor):
-                continue
-            t = t.detach().contiguous()
+        tensors = [t.detach().contiguous() for t in vals if isinstance(t, torch.Tensor)]
+        if self.cuda and len(tensors) > 1:
+            # all tensors of a stage boundary go out as one grouped NCCL call
+            for w in dist.batch_isend_irecv([dist.P2POp(dist.isend, t, peer, group, tag) for t in tensors]):
+                w.wait()                 # stream-level wait only; the host does not block
+            return
+        for t in tensors:
             w = dist.isend(t, dst=peer, group=group, tag=tag)
             if self.cuda:
-                w.wait()                 # stream-level wait only; the host does not block
+                w.wait()
             else:
                 self.pending.append(_Hold(w, t))
 
@@ -700,6 +723,11 @@ class DagExecutor:
         else:
             metas = self.shape_ref[consumer.node_meta["fwd_uid"]]
         bufs, works = [], []
+        if self.cuda and len(metas) > 1:
+            bufs = [torch.empty(shape, dtype=dtype, device=a.device) for shape, dtype in metas]
+            for w in dist.batch_isend_irecv([dist.P2POp(dist.irecv, b, peer, group, tag) for b in bufs]):
+                w.wait()
+            metas = []
         for shape, dtype in metas:
             buf = torch.empty(shape, dtype=dtype, device=a.device)
             w = dist.irecv(buf, src=peer, group=group, tag=tag)

@@ -59,7 +59,8 @@ def _worker(rank, world, schedule, num_stages, global_batch, dp, steps, ckpt=Fal
         if first is None:
             first = ([float(l) for l in losses], dict(actor.last_grads))
     params = {k: v.detach().clone() for k, v in actor.named_parameters().items()}
-    return {"losses": first[0], "grads": first[1], "params": params, "dp_rank": layout.dp_rank}
+    return {"losses": first[0], "grads": first[1], "params": params, "dp_rank": layout.dp_rank,
+            "bucket_keys": list(actor.buckets)}
 
 
 def _check(results, ref, dp, atol=1e-5, check_params=False):
@@ -124,6 +125,20 @@ def test_dp2_zero_matches_single_process(tmp_path, flags):
     sched = _sched([[0, 1]], 2, extra=[{"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1],
                                         "gather_stream": "dp_stream", "reduce_stream": "dp_stream", **flags}])
     res = run_ranks(2, _worker, (sched, 1, 8, 2, 2), tmp_path)
+    _check(res, _reference(8, steps=2), dp=2, check_params=True)
+
+
+@pytest.mark.parametrize("flags", [{}, {"shard_grads": True, "shard_params": True}])
+def test_pp2_dp2_1f1b_with_parameter_buckets_matches_single_process(tmp_path, flags):
+    """Pipeline messages meet bucket chains: ``replicate.bucket_size`` splits each stage into per-bucket nodes, so
+    sends leave from the last bucket of a chain and receives feed the first (plain and ZeRO-3 buckets)."""
+    from piper_b200.compiler.builders import build_1f1b_schedule
+
+    extra = [{"op": "replicate", "filter": {"PP": i}, "devices": d, "reduce_stream": "dp_stream",
+              "gather_stream": "gather_stream", "bucket_size": 1, **flags} for i, d in enumerate([[0, 2], [1, 3]])]
+    sched = _sched([[0, 2], [1, 3]], 2, extra=extra, order=build_1f1b_schedule(2, 2))
+    res = run_ranks(4, _worker, (sched, 2, 8, 2, 2), tmp_path, timeout=600)
+    assert any("bucket" in k for r in res for k in r.get("bucket_keys", []))
     _check(res, _reference(8, steps=2), dp=2, check_params=True)
 
 

@@ -130,16 +130,19 @@ def test_zero_reduce_and_gather_kernels_with_emulated_ranks(dp):
     # gather: every rank's shard back into a full buffer, with and without a skipped parameter
     shards = [st[r]["shard_p"] for r in range(dp)]
     full = torch.zeros(numel, device=dev, dtype=torch.bfloat16)
-    lib.zero_gather(ptr(shards), full, table, dp, -1, None, 16)
+    lib.zero_gather(ptr(shards), full, table, dp, -1, -1, None, 16)
     torch.cuda.synchronize()
     for s in slots:
         assert torch.equal(full[s.offset:s.offset + s.numel], full_params[0][s.offset:s.offset + s.numel])
     full.zero_()
-    lib.zero_gather(ptr(shards), full, table, dp, 0, None, 16)
+    lib.zero_gather(ptr(shards), full, table, dp, 0, -1, None, 16)
     torch.cuda.synchronize()
     assert torch.count_nonzero(full[:slots[0].numel]) == 0
     s = slots[2]
     assert torch.equal(full[s.offset:s.offset + s.numel], full_params[0][s.offset:s.offset + s.numel])
+    lib.zero_gather(ptr(shards), full, table, dp, -1, 0, None, 16)       # then only the parameter left out
+    torch.cuda.synchronize()
+    assert torch.equal(full[:slots[0].numel], full_params[0][:slots[0].numel])
 
 
 def _dp_worker(rank, world, fused, steps, mode="allreduce"):

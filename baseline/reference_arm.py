@@ -227,6 +227,8 @@ def run(args) -> dict | None:
         return None
 
     pp, dp = LAYOUTS[n]
+    if os.environ.get("PIPER_BENCH_LAYOUT"):           # smoke runs only
+        pp, dp = (int(v) for v in os.environ["PIPER_BENCH_LAYOUT"].lower().split("x"))
     mbs = GLOBAL_SEQS // dp
     os.makedirs(rdv, exist_ok=True)
     sched_file = os.path.join(rdv, f"llama_pp{pp}_dp{dp}_1f1b_mbs{mbs}.json")

@@ -54,6 +54,10 @@ def build_job(config: str, n_gpus: int, model: str, bucket_mb: int) -> dict:
     from piper_b200.compiler.builders import build_1f1b_schedule, build_dualpipev_schedule
 
     pp, dp = LAYOUTS[config][n_gpus]
+    if os.environ.get("PIPER_BENCH_LAYOUT"):           # smoke runs only: "PPxDP" in place of the config's layout
+        pp, dp = (int(v) for v in os.environ["PIPER_BENCH_LAYOUT"].lower().split("x"))
+        if pp * dp != n_gpus:
+            raise SystemExit(f"PIPER_BENCH_LAYOUT={pp}x{dp} does not use {n_gpus} GPUs")
     sched: list = []
     if config.startswith("llama"):
         from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer, balanced_stage_layers
@@ -210,7 +214,7 @@ def run_ours(args) -> dict:
 
     # the same DAG with every collective lowered to NCCL calls, for the fused-versus-NCCL end-to-end gain
     nccl_tps = None
-    if args.nccl_arm and n > 1 and (actor.fused is not None or actor.ep_fused is not None) and peak_gb < 80:
+    if args.nccl_arm and n > 1 and (actor.fused is not None or actor.ep_fused is not None) and peak_gb < 120:
         import gc
 
         from piper_b200.state import piper_metadata
@@ -256,6 +260,7 @@ def run_ours(args) -> dict:
                    "num_microbatches": mbs, "parallelism": job["parallelism"], "schedule": job["schedule"],
                    "stage_layers": job["stage_layers"], "optimizer": "Adam, fp32 master + moments",
                    "bucket_size_mb": args.bucket_mb if dp > 1 else None,
+                   **({"layout_override": os.environ["PIPER_BENCH_LAYOUT"]} if os.environ.get("PIPER_BENCH_LAYOUT") else {}),
                    "l2": "per-step working set >> 126 MB L2, no flush between steps"},
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
@@ -286,9 +291,12 @@ def main() -> int:
     ap.add_argument("--config", default="llama_pp4dp2", choices=CONFIGS)
     ap.add_argument("--model", default=None, help="model size override (smaller shapes are for smoke runs only)")
     ap.add_argument("--bucket-mb", type=int, default=1000, help="replicate.bucket_size of the data-parallel buckets")
+    ap.add_argument("--layout", default=None, help="PPxDP in place of the configuration's layout (smoke runs only)")
     ap.add_argument("--nccl-arm", action=argparse.BooleanOptionalAction, default=True,
                     help="also time the NCCL lowering of the same DAG (multi-GPU runs with a fused path)")
     args = ap.parse_args()
+    if args.layout:
+        os.environ["PIPER_BENCH_LAYOUT"] = args.layout
     if args.gpus not in LAYOUTS[args.config]:
         raise SystemExit(f"--gpus must be one of {sorted(LAYOUTS[args.config])} for --config {args.config}")
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))

@@ -39,8 +39,8 @@ CONFIGS = ("llama_pp4dp2", "llama_pp2dp4_zero3", "qwen_dualpipev", "qwen_zero3_e
 LAYOUTS = {
     "llama_pp4dp2": {1: (1, 1), 2: (2, 1), 4: (4, 1), 8: (4, 2)},
     "llama_pp2dp4_zero3": {2: (1, 2), 4: (2, 2), 8: (2, 4)},
-    "qwen_dualpipev": {4: (2, 2), 8: (2, 4)},
-    "qwen_zero3_ep4": {4: (2, 2), 8: (2, 4)},
+    "qwen_dualpipev": {2: (1, 2), 4: (2, 2), 8: (2, 4)},
+    "qwen_zero3_ep4": {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)},
 }
 N1_RECORD = os.path.join(os.environ.get("TMPDIR", "/tmp"), "piper_bench_llama_pp4dp2_n1.json")
 

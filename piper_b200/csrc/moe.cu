@@ -3,6 +3,8 @@
 // combine, and the backward passes.  One warp handles one token.
 #include "moe.h"
 
+#include "ptx.cuh"
+
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -146,19 +148,25 @@ struct alignas(16) vec16 { uint4 v; };
 // One warp per token: claims a row per entry, copies the token row there.
 __global__ void permute_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
                                const int* __restrict__ g_start, int* __restrict__ cursor, int* __restrict__ pos,
-                               __nv_bfloat16* __restrict__ rows, long long T, int D, int k) {
+                               __nv_bfloat16* __restrict__ rows, long long T, int D, int k, int E, long long rows_cap,
+                               int* status) {
   const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + t * D);
   for (int j = 0; j < k; ++j) {
-    int r = 0;
+    int r = -1;
     if (lane == 0) {
       const int e = idx[t * k + j];
-      r = g_start[e] + atomicAdd(cursor + e, 1);
-      pos[t * k + j] = r;
+      if (e >= 0 && e < E) r = g_start[e] + atomicAdd(cursor + e, 1);
+      if (r < 0 || r >= rows_cap) {             // rejected: recorded, the copy is skipped
+        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        r = -1;
+      }
+      pos[t * k + j] = r < 0 ? 0 : r;
     }
     r = __shfl_sync(0xffffffffu, r, 0);
+    if (r < 0) continue;
     uint4* dst = reinterpret_cast<uint4*>(rows + static_cast<long long>(r) * D);
     for (int i = lane; i < D / 8; i += 32) dst[i] = src[i];
   }
@@ -166,10 +174,15 @@ __global__ void permute_kernel(const __nv_bfloat16* __restrict__ x, const int* _
 
 // Zeroes rows [g_start + counts, g_start + g_len) of every group.
 __global__ void zero_padding_kernel(__nv_bfloat16* __restrict__ rows, const int* __restrict__ g_start,
-                                    const int* __restrict__ g_len, const int* __restrict__ counts, int D) {
+                                    const int* __restrict__ g_len, const int* __restrict__ counts, int D,
+                                    long long rows_cap, int* status) {
   const int g = blockIdx.x;
   const int first = g_start[g] + counts[g];
   const int last = g_start[g] + g_len[g];
+  if (counts[g] < 0 || g_start[g] < 0 || last < first || last > rows_cap) {
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+    return;                                   // a segment outside the buffer is left alone
+  }
   const uint4 z = make_uint4(0, 0, 0, 0);
   const long long nvec = static_cast<long long>(last - first) * (D / 8);
   uint4* base = reinterpret_cast<uint4*>(rows + static_cast<long long>(first) * D);
@@ -177,14 +190,20 @@ __global__ void zero_padding_kernel(__nv_bfloat16* __restrict__ rows, const int*
 }
 
 __global__ void permute_bwd_kernel(const __nv_bfloat16* __restrict__ drows, const int* __restrict__ pos,
-                                   __nv_bfloat16* __restrict__ dx, long long T, int D, int k) {
+                                   __nv_bfloat16* __restrict__ dx, long long T, int D, int k, long long rows_cap,
+                                   int* status) {
   const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
   for (int i = lane; i < D / 8; i += 32) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {
-      const uint4 q = reinterpret_cast<const uint4*>(drows + static_cast<long long>(pos[t * k + j]) * D)[i];
+      const long long r = pos[t * k + j];
+      if (r < 0 || r >= rows_cap) {             // a row outside the buffer contributes nothing
+        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        continue;
+      }
+      const uint4 q = reinterpret_cast<const uint4*>(drows + r * D)[i];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -203,7 +222,7 @@ __global__ void permute_bwd_kernel(const __nv_bfloat16* __restrict__ drows, cons
 
 __global__ void combine_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ pos,
                                const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, long long T,
-                               int D, int k) {
+                               int D, int k, long long rows_cap, int* status) {
   const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -211,7 +230,12 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ rows, const int
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int j = 0; j < k; ++j) {
       const float w = weights[t * k + j];
-      const uint4 q = reinterpret_cast<const uint4*>(rows + static_cast<long long>(pos[t * k + j]) * D)[i];
+      const long long r = pos[t * k + j];
+      if (r < 0 || r >= rows_cap) {
+        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        continue;
+      }
+      const uint4 q = reinterpret_cast<const uint4*>(rows + r * D)[i];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -231,13 +255,20 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ rows, const int
 __global__ void combine_bwd_kernel(const __nv_bfloat16* __restrict__ rows, const __nv_bfloat16* __restrict__ dout,
                                    const int* __restrict__ pos, const float* __restrict__ weights,
                                    __nv_bfloat16* __restrict__ drows, float* __restrict__ dweights, long long T,
-                                   int D, int k) {
+                                   int D, int k, long long rows_cap, int* status) {
   const long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
   for (int j = 0; j < k; ++j) {
     const float w = weights[t * k + j];
     const long long r = pos[t * k + j];
+    if (r < 0 || r >= rows_cap) {
+      if (lane == 0) {
+        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        dweights[t * k + j] = 0.f;
+      }
+      continue;
+    }
     float dot = 0.f;
     for (int i = lane; i < D / 8; i += 32) {
       const uint4 g = reinterpret_cast<const uint4*>(dout + t * D)[i];
@@ -295,41 +326,46 @@ int moe_group_table(const int* counts, int num_groups, int experts, const int* r
 }
 
 int moe_permute(const void* x, const int* idx, const int* g_start, const int* g_len, const int* counts, int* cursor,
-                int* pos, void* rows, long long T, int D, int E, int k, cudaStream_t st) {
+                int* pos, void* rows, long long T, int D, int E, int k, long long rows_cap, int* status,
+                cudaStream_t st) {
   if (D % 8 != 0) return -1;
   if (T > 0)
     permute_kernel<<<warps_grid(T, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), idx, g_start, cursor,
-                                                       pos, static_cast<__nv_bfloat16*>(rows), T, D, k);
-  zero_padding_kernel<<<E, 256, 0, st>>>(static_cast<__nv_bfloat16*>(rows), g_start, g_len, counts, D);
+                                                       pos, static_cast<__nv_bfloat16*>(rows), T, D, k, E, rows_cap,
+                                                       status);
+  zero_padding_kernel<<<E, 256, 0, st>>>(static_cast<__nv_bfloat16*>(rows), g_start, g_len, counts, D, rows_cap, status);
   return PIPER_LAUNCH_OK();
 }
 
-int moe_permute_bwd(const void* drows, const int* pos, void* dx, long long T, int D, int k, cudaStream_t st) {
+int moe_permute_bwd(const void* drows, const int* pos, void* dx, long long T, int D, int k, long long rows_cap,
+                    int* status, cudaStream_t st) {
   if (D % 8 != 0) return -1;
   if (T == 0) return 0;
   permute_bwd_kernel<<<warps_grid(T, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(drows), pos,
-                                                         static_cast<__nv_bfloat16*>(dx), T, D, k);
+                                                         static_cast<__nv_bfloat16*>(dx), T, D, k, rows_cap, status);
   return PIPER_LAUNCH_OK();
 }
 
 int moe_combine(const void* rows, const int* pos, const float* weights, void* out, long long T, int D, int k,
-                cudaStream_t st) {
+                long long rows_cap, int* status, cudaStream_t st) {
   if (D % 8 != 0) return -1;
   if (T == 0) return 0;
   combine_kernel<<<warps_grid(T, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(rows), pos, weights,
-                                                     static_cast<__nv_bfloat16*>(out), T, D, k);
+                                                     static_cast<__nv_bfloat16*>(out), T, D, k, rows_cap, status);
   return PIPER_LAUNCH_OK();
 }
 
 int moe_combine_bwd(const void* rows, const void* dout, const int* pos, const float* weights, void* drows,
                     float* dweights, const int* g_start, const int* g_len, const int* counts, int num_groups,
-                    long long T, int D, int k, cudaStream_t st) {
+                    long long T, int D, int k, long long rows_cap, int* status, cudaStream_t st) {
   if (D % 8 != 0) return -1;
   if (T > 0)
     combine_bwd_kernel<<<warps_grid(T, 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(rows),
                                                            static_cast<const __nv_bfloat16*>(dout), pos, weights,
-                                                           static_cast<__nv_bfloat16*>(drows), dweights, T, D, k);
-  zero_padding_kernel<<<num_groups, 256, 0, st>>>(static_cast<__nv_bfloat16*>(drows), g_start, g_len, counts, D);
+                                                           static_cast<__nv_bfloat16*>(drows), dweights, T, D, k,
+                                                           rows_cap, status);
+  zero_padding_kernel<<<num_groups, 256, 0, st>>>(static_cast<__nv_bfloat16*>(drows), g_start, g_len, counts, D,
+                                                  rows_cap, status);
   return PIPER_LAUNCH_OK();
 }
 

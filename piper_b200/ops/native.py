@@ -76,6 +76,7 @@ def status_tensor(device: torch.device | None = None) -> torch.Tensor:
         # word 0 is the status; a peer wait that runs out leaves (tag, flag index, wanted value) in words 1..3
         _status_detail[idx] = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", idx))
         t = _status[idx] = _status_detail[idx][:1]
+        lib().set_status_word(t)          # kernels whose bindings take no status argument report into it too
     return t
 
 

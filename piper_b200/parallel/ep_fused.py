@@ -357,7 +357,9 @@ class FusedExpertRuntime:
             b = p.buf_id("recv", ex.slot)
             lib.ep_wait_table(p.flags_local, p.off(b, READY), p.meta[ex.slot], g_start, g_len, rc, self.ep, p.cap_src,
                               ex.recv_use, self.timeout_s, status)
-            ex.table = (g_start, g_len, rc)
+            # the senders' own segment starts travel in the slot's meta block, which the next exchange in this
+            # slot overwrites: keep a copy for the two returns of this exchange
+            ex.table = (g_start, g_len, rc, p.meta[ex.slot][G:2 * G].clone())
             out[ti] = p.recv[ex.slot]
             if ci is not None:
                 out[ci] = rc
@@ -369,8 +371,8 @@ class FusedExpertRuntime:
             b = p.buf_id(name, i)
             use = p.next_use(b)
             dst = p.ret_ptrs[i] if kind == "F_out" else p.gret_ptrs[i]
-            g_start, g_len, _ = ex.table
-            lib.ep_block_push(rows, g_start, g_len, p.meta[ex.slot][G:2 * G], p.El, 0, p.cap_loc, dst, p.flags_ptrs,
+            g_start, g_len, _, home = ex.table
+            lib.ep_block_push(rows, g_start, g_len, home, p.El, 0, p.cap_loc, dst, p.flags_ptrs,
                               p.flags_local, p.off(b, FREE), self._free_needed(b, use), p.off(b, READY), use,
                               p.counters[b:b + 1], p.aborts[b:b + 1], self.me, self.ep, self.timeout_s, status, self.num_ctas)
             lib.ep_wait(p.flags_local, p.off(b, READY), self.ep, use, self.timeout_s, status, 4 if kind == "F_out" else 6, None)
@@ -394,6 +396,7 @@ class FusedExpertRuntime:
         if ex.split_backward:
             # the deferred weight-gradient GEMMs read these rows long after the ring has moved on
             out[ti] = p.gin[i].clone()
+            out[ti].record_stream(torch.cuda.default_stream(dev))    # allocated on this stream, read by compute kernels
             self._signal(b, use)
         else:
             out[ti] = p.gin[i]

@@ -390,14 +390,21 @@ class _ActorClass:
         rt = runtime()
         name = self._options.get("name")
         methods = [m for m in dir(self._cls) if callable(getattr(self._cls, m, None)) and not m.startswith("__")]
-        rank = rt.place("actor", self._cls, args, kwargs, self._options)
-        actor_id = rt.new_id()
-        if name is not None:
-            existing = rt.request(0, "name_register", name, rank, actor_id, methods,
-                                  bool(self._options.get("get_if_exists", False))).result()
+        if name is not None and self._options.get("get_if_exists", False):
+            existing = rt.request(0, "name_lookup", name).result()
             if existing is not None:
                 return ActorHandle(*existing)
+        rank = rt.place("actor", self._cls, args, kwargs, self._options)
+        actor_id = rt.new_id()
         rt.request(rank, "create", actor_id, _dumps((self._cls, args, kwargs))).result()
+        if name is not None:
+            # the name becomes visible only once the actor exists, so a lookup never returns a handle that
+            # cannot be called yet
+            existing = rt.request(0, "name_register", name, rank, actor_id, methods,
+                                  bool(self._options.get("get_if_exists", False))).result()
+            if existing is not None:                      # somebody else registered the name first
+                rt.request(rank, "kill", actor_id).result()
+                return ActorHandle(*existing)
         return ActorHandle(rank, actor_id, methods)
 
     def __call__(self, *a, **k):

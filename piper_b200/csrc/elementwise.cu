@@ -5,6 +5,8 @@
 // 16-byte vectors and keep fp32 math in registers; none allocates.
 #include "elementwise.h"
 
+#include "ptx.cuh"
+
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -640,7 +642,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ tokens,
   const long long row = blockIdx.x;
   long long tok = tokens[row];
   if (tok < 0 || tok >= V) {   // recorded, not trapped
-    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 3);
+    if (threadIdx.x == 0) report_bad_argument(status, 41, row, tok);
     tok = 0;
   }
   const bf16x8* src = reinterpret_cast<const bf16x8*>(table + tok * D);

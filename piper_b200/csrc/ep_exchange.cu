@@ -61,7 +61,7 @@ __global__ void ep_prepare_kernel(const int* __restrict__ counts, const int* __r
     }
     const bool over = run > cap_src;
     ctl[1 + d] = over ? 1 : 0;
-    if (over) atomicCAS(status, 0, kStatusBadArgument);
+    if (over) report_bad_argument(status, 21, d, run);
     // meta block of a slot: counts [ep * El] followed by the senders' local segment starts [ep * El]
     for (int l = 0; l < experts_local; ++l) {
       const int e = d * experts_local + l;
@@ -99,10 +99,10 @@ ep_dispatch_push_kernel(const __nv_bfloat16* __restrict__ x, const int* __restri
           row_l = my_rank * cap_src + seg_off[e] + c;
           p = g_start_loc[e] + c;
         } else if (ctl[1 + d] == 0) {
-          atomicCAS(status, 0, kStatusBadArgument);      // more rows for e than its count announced
+          report_bad_argument(status, 23, e, c);         // more rows for e than its count announced
         }
       } else {
-        atomicCAS(status, 0, kStatusBadArgument);        // expert index out of range
+        report_bad_argument(status, 22, e, t);           // expert index out of range
       }
       pos_loc[t * k + lane] = p < 0 ? 0 : p;
     }
@@ -193,7 +193,7 @@ ep_block_push_kernel(const __nv_bfloat16* __restrict__ src, const int* __restric
       int len = seg_len[g];
       const long long s0 = seg_src[g], d0 = static_cast<long long>(seg_dst[g]) + dst_bias;
       if (len < 0 || s0 < 0 || s0 + len > src_rows || d0 < 0 || d0 + len > dst_rows) {
-        atomicCAS(status, 0, kStatusBadArgument);       // a segment outside its buffer is not copied
+        report_bad_argument(status, 24, g, d0 + len);   // a segment outside its buffer is not copied
         len = 0;
       }
       run += (len + 31) / 32;

@@ -160,7 +160,7 @@ __global__ void permute_kernel(const __nv_bfloat16* __restrict__ x, const int* _
       const int e = idx[t * k + j];
       if (e >= 0 && e < E) r = g_start[e] + atomicAdd(cursor + e, 1);
       if (r < 0 || r >= rows_cap) {             // rejected: recorded, the copy is skipped
-        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        report_bad_argument(status, 31, e, r);
         r = -1;
       }
       pos[t * k + j] = r < 0 ? 0 : r;
@@ -180,7 +180,7 @@ __global__ void zero_padding_kernel(__nv_bfloat16* __restrict__ rows, const int*
   const int first = g_start[g] + counts[g];
   const int last = g_start[g] + g_len[g];
   if (counts[g] < 0 || g_start[g] < 0 || last < first || last > rows_cap) {
-    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+    if (threadIdx.x == 0) report_bad_argument(status, 35, g, last);
     return;                                   // a segment outside the buffer is left alone
   }
   const uint4 z = make_uint4(0, 0, 0, 0);
@@ -200,7 +200,7 @@ __global__ void permute_bwd_kernel(const __nv_bfloat16* __restrict__ drows, cons
     for (int j = 0; j < k; ++j) {
       const long long r = pos[t * k + j];
       if (r < 0 || r >= rows_cap) {             // a row outside the buffer contributes nothing
-        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        report_bad_argument(status, 32, t, r);
         continue;
       }
       const uint4 q = reinterpret_cast<const uint4*>(drows + r * D)[i];
@@ -232,7 +232,7 @@ __global__ void combine_kernel(const __nv_bfloat16* __restrict__ rows, const int
       const float w = weights[t * k + j];
       const long long r = pos[t * k + j];
       if (r < 0 || r >= rows_cap) {
-        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        report_bad_argument(status, 33, t, r);
         continue;
       }
       const uint4 q = reinterpret_cast<const uint4*>(rows + r * D)[i];
@@ -264,7 +264,7 @@ __global__ void combine_bwd_kernel(const __nv_bfloat16* __restrict__ rows, const
     const long long r = pos[t * k + j];
     if (r < 0 || r >= rows_cap) {
       if (lane == 0) {
-        if (status != nullptr) atomicCAS(status, 0, kStatusBadArgument);
+        report_bad_argument(status, 34, t, r);
         dweights[t * k + j] = 0.f;
       }
       continue;

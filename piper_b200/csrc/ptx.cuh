@@ -20,6 +20,18 @@ enum : int {
   kStatusBadArgument = 3,   // in-kernel argument check failed
 };
 
+// Records a rejected argument: the status word is the first of four ints; the first kernel to fail also leaves
+// (tag of the check, two values that describe it) in the other three.  Tags: 21-24 expert exchange (region
+// overflow, expert index, row count, segment range), 31-35 permutation kernels (permute, its gradient, combine,
+// its gradient, padding), 41 embedding.
+__device__ __forceinline__ void report_bad_argument(int* status, int tag, long long a, long long b) {
+  if (status != nullptr && atomicCAS(status, 0, kStatusBadArgument) == 0) {
+    status[1] = tag;
+    status[2] = static_cast<int>(a);
+    status[3] = static_cast<int>(b);
+  }
+}
+
 // Upper bound on polls of one wait.  try_wait itself blocks for a
 // hardware-defined slice, so this is on the order of seconds.
 constexpr uint32_t kMaxMbarPolls = 1u << 24;

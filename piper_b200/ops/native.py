@@ -95,7 +95,7 @@ def check_status(device: torch.device | None = None, *, reset: bool = True) -> N
     t = status_tensor(device)
     code = int(t.item())
     if code != 0:
-        detail = f" (wait tag, flag index, wanted value: {status_detail(device)})" if code == 2 else ""
+        detail = f" (tag of the check or wait and two values describing it: {status_detail(device)})"
         if reset:
             t.zero_()
         raise_for_status(code, detail)
@@ -151,7 +151,7 @@ class StatusMonitor:
         if code != 0:
             detail = ""
             if self.source is not None:
-                if self.cuda and code == 2:
-                    detail = f" (wait tag, flag index, wanted value: {status_detail(self.device)})"
+                if self.cuda:
+                    detail = f" (tag of the check or wait and two values describing it: {status_detail(self.device)})"
                 self.source.zero_()
             raise_for_status(code, detail)

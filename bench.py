@@ -83,7 +83,11 @@ def build_job(config: str, n_gpus: int, model: str, bucket_mb: int) -> dict:
                 "parallelism": f"pp{pp}dp{dp}" + ("-zero3" if zero3 else "")}
     from piper_b200.models.qwen3 import QWEN3_CONFIGS, PiperQwen3Model
 
-    cfg = QWEN3_CONFIGS[model or "30B-A3B"]
+    import dataclasses
+
+    # the configuration asks for a router that spreads tokens near-uniformly at initialisation: frozen-noise
+    # top-k gating (see Qwen3Config.router_jitter_std)
+    cfg = dataclasses.replace(QWEN3_CONFIGS[model or "30B-A3B"], router_jitter_std=8.0)
     mbs = 8
     v = config == "qwen_dualpipev"
     stages = 2 * pp if v else pp

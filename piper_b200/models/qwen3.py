@@ -41,6 +41,11 @@ class Qwen3Config:
     norm_eps: float = 1e-6
     rope_theta: float = 1000000.0
     max_seq_len: int = 4096
+    # Noisy top-k gating with frozen noise: a fixed N(0, std) table [seq, experts] added to the router logits.
+    # A randomly initialised deep MoE sends almost every token to the same few experts (the residual streams of
+    # different positions are strongly correlated before any training); benchmark runs set a std that dominates
+    # the initial logits so that the load over experts is near-uniform from the first step.  0 disables it.
+    router_jitter_std: float = 0.0
 
 
 QWEN3_CONFIGS = {
@@ -84,8 +89,11 @@ class MoE(nn.Module):
         self.gate = Linear(cfg.dim, cfg.num_experts)
         self.experts = GroupedExperts(cfg.dim, cfg.moe_hidden, cfg.num_experts)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        weights, idx, counts = moe_ops.moe_route(self.gate(x), self.top_k, self.renorm)
+    def forward(self, x: torch.Tensor, jitter: Optional[torch.Tensor] = None) -> torch.Tensor:
+        logits = self.gate(x)
+        if jitter is not None:
+            logits = logits + jitter
+        weights, idx, counts = moe_ops.moe_route(logits, self.top_k, self.renorm)
         rows, pos, g_start, g_len, ep_counts = moe_ops.moe_dispatch(x, idx, counts)
         with annotate(EP_TAG):
             out_rows = self.experts(rows, ep_counts)
@@ -102,14 +110,14 @@ class Qwen3Block(nn.Module):
         self.moe = MoE(cfg) if cfg.moe_enabled else None
         self.feed_forward = None if cfg.moe_enabled else FeedForward(cfg.dim, cfg.ffn_hidden)
 
-    def forward(self, h, delta, cos, sin, batch: int, seq: int):
+    def forward(self, h, delta, cos, sin, batch: int, seq: int, jitter=None):
         if delta is None:
             y = self.attention_norm(h)
         else:
             y, h = self.attention_norm(delta, h)
         a = self.attention(y, cos, sin, batch, seq)
         y, h = self.ffn_norm(a, h)
-        return h, (self.moe(y) if self.moe is not None else self.feed_forward(y))
+        return h, (self.moe(y, jitter) if self.moe is not None else self.feed_forward(y))
 
 
 class PiperQwen3Model(nn.Module):
@@ -128,27 +136,40 @@ class PiperQwen3Model(nn.Module):
         self.output = Linear(cfg.dim, cfg.vocab_size)
         self.register_buffer("rope_cos", torch.empty(self.seq_len, cfg.head_dim // 2), persistent=False)
         self.register_buffer("rope_sin", torch.empty(self.seq_len, cfg.head_dim // 2), persistent=False)
+        self.use_jitter = cfg.router_jitter_std > 0 and cfg.moe_enabled
+        if self.use_jitter:
+            self.register_buffer("router_jitter", torch.empty(self.seq_len, cfg.num_experts), persistent=False)
 
     @staticmethod
     def const_attrs(cfg: Qwen3Config, seq_len: int, device=None) -> dict:
         cos, sin = ops.rope_tables(cfg.head_dim, seq_len, cfg.rope_theta, device=device)
-        return {"rope_cos": cos, "rope_sin": sin}
+        out = {"rope_cos": cos, "rope_sin": sin}
+        if cfg.router_jitter_std > 0 and cfg.moe_enabled:
+            g = torch.Generator().manual_seed(20240229)
+            noise = torch.randn(seq_len, cfg.num_experts, generator=g) * cfg.router_jitter_std
+            out["router_jitter"] = noise.to(torch.bfloat16).to(device) if device is not None else noise.to(torch.bfloat16)
+        return out
 
     def load_const_attrs(self, seq_len: Optional[int] = None) -> None:
         c = self.const_attrs(self.cfg, seq_len or self.seq_len, self.rope_cos.device)
         self.rope_cos, self.rope_sin = c["rope_cos"].float(), c["rope_sin"].float()
+        if self.use_jitter:
+            self.router_jitter = c["router_jitter"].to(self.rope_cos.device)
 
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         batch, seq = tokens.shape
         n = len(self.layers)
         h = delta = out = None
+        jitter = None
+        if self.use_jitter:
+            jitter = self.router_jitter if batch == 1 else self.router_jitter.repeat(batch, 1)
         for stage in range(self.num_stages):
             lo, hi = stage * n // self.num_stages, (stage + 1) * n // self.num_stages
             with annotate(PP_TAG):
                 if stage == 0:
                     h = self.tok_embeddings(tokens.reshape(-1))
                 for i in range(lo, hi):
-                    h, delta = self.layers[i](h, delta, self.rope_cos, self.rope_sin, batch, seq)
+                    h, delta = self.layers[i](h, delta, self.rope_cos, self.rope_sin, batch, seq, jitter)
                 if stage == self.num_stages - 1:
                     y, h = self.norm(delta, h)
                     out = self.output(y).view(batch, seq, -1)

@@ -22,6 +22,8 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 OBJ = ROOT / "lib" / "obj"
 LIB = ROOT / "lib" / "libpiper_b200.so"
+PLAN_SRC = CSRC / "plan" / "plan_executor.cpp"
+PLAN_LIB = ROOT / "lib" / "piper_plan.so"          # CPython extension module (pybind11): the launch-plan executor
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -98,7 +100,35 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         finally:
             if tmp.exists():
                 tmp.unlink()
+    build_plan_executor(force=force, verbose=verbose)
     return LIB
+
+
+def build_plan_executor(force: bool = False, verbose: bool = False) -> Path:
+    """The launch-plan executor is a separate CPython extension module: it calls back into Python."""
+    import sysconfig
+
+    import pybind11
+
+    if not force and PLAN_LIB.exists() and PLAN_LIB.stat().st_mtime >= PLAN_SRC.stat().st_mtime:
+        return PLAN_LIB
+    inc, libdirs, abi = _torch_paths()
+    tmp = PLAN_LIB.with_name(PLAN_LIB.name + f".{os.getpid()}.tmp")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-fvisibility=hidden",
+           "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
+    for i in inc:
+        cmd += ["-isystem", i]
+    cmd += [str(PLAN_SRC), "-o", str(tmp)]
+    for d in libdirs:
+        cmd += [f"-L{d}", f"-Wl,-rpath,{d}"]
+    cmd += ["-lc10", "-lc10_cuda", "-lcudart"]
+    try:
+        _run(cmd, verbose)
+        os.replace(tmp, PLAN_LIB)
+    finally:
+        if tmp.exists():
+            tmp.unlink()
+    return PLAN_LIB
 
 
 def main(argv=None) -> int:

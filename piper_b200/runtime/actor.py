@@ -165,6 +165,7 @@ class PiperActor:
         computes = [u for u in self.order if dag.nodes[u].node_kind == COMPUTE]
         self._last_compute_uid = computes[-1] if computes else None
         self._tail_events = None
+        self._plan = None
 
     def _bucket_modes(self, dag: TrainingDAG) -> dict:
         modes: dict[str, str] = {}
@@ -285,6 +286,28 @@ class PiperActor:
         self.iteration += 1
         return out
 
+    def native_plan(self, executor):
+        """The C++ replay loop over this actor's dispatch order (built once); ``None`` selects the Python loop
+        (``PIPER_NATIVE_EXECUTOR=0``, CPU runs, or the extension module is missing on a CPU-only machine)."""
+        if self._plan is False:
+            return None
+        if self._plan is None:
+            import os
+            mod = _load_plan_module() if os.environ.get("PIPER_NATIVE_EXECUTOR", "1") != "0" else None
+            if mod is None:
+                if os.environ.get("PIPER_NATIVE_EXECUTOR", "1") != "0":
+                    raise RuntimeError("the launch-plan executor piper_plan.so is missing; build it with "
+                                       "`python -m piper_b200.build`")
+                self._plan = False
+                return None
+            streams, node_stream, waits = executor.static_waits(self.order)
+            labels = [_node_label(self.dag.nodes[u]) for u in self.order]
+            self._plan_streams = streams          # keeps the torch stream objects alive
+            self._plan = mod.PlanExecutor(self.device.index if self.device.index is not None else
+                                          torch.cuda.current_device(), [int(s.cuda_stream) for s in streams],
+                                          node_stream, waits, labels, not self.no_nvtx)
+        return self._plan
+
     def comm_tail_ms(self) -> float:
         """Device time of the last step between the end of its last compute node and the end of the step: the
         part of gradient synchronisation and optimizer work that no backward kernel was left to hide."""
@@ -341,6 +364,24 @@ class PiperActor:
             for s in st.slots:
                 out[s.fqn] = st.flat_grads[s.offset:s.offset + s.numel].view(s.shape)
         return out
+
+
+def _node_label(node: TrainingDAGNode) -> str:
+    tags = ",".join(f"{k}={v}" for k, v in sorted(node.tag.items(), key=lambda kv: kv[0]) if v is not None)
+    return f"{node.node_kind}:{tags}:uid{node.uid}"
+
+
+def _load_plan_module():
+    """The C++ launch-plan executor (``csrc/plan/plan_executor.cpp``), built next to the kernel library."""
+    import importlib.util
+
+    path = native.lib_path().with_name("piper_plan.so")
+    if not path.exists():
+        return None
+    spec = importlib.util.spec_from_file_location("piper_plan", str(path))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def _my_ep_ranks(ep: dict, rank: int) -> list:
@@ -465,63 +506,52 @@ class DagExecutor:
                     s.wait_stream(cur)
             for s in a._channel_streams.values():
                 s.wait_stream(cur)
-        tail0 = None
-        for uid in a.order:
-            node = self.dag.nodes[uid]
-            kind = node.node_kind
-            label = None
-            if self.cuda and (not a.no_nvtx or a.profile_nodes):
-                tags = ",".join(f"{k}={v}" for k, v in sorted(node.tag.items(), key=lambda kv: kv[0]) if v is not None)
-                label = f"{kind}:{tags}:uid{uid}"
-                if not a.no_nvtx:
-                    torch.cuda.nvtx.range_push(label)
-            rf = torch.profiler.record_function(label) if (a.profile_nodes and label) else _NullCtx()
-            with rf, (torch.cuda.stream(self._stream(node)) if self.cuda else _NullCtx()):
-                self._wait_preds(node)
-                t_node = time.perf_counter()
-                if a.time_nodes and self.cuda:
-                    ev0 = torch.cuda.Event(enable_timing=True)
-                    ev0.record(self._stream(node))
-                if kind == COMPUTE:
-                    sub = node.compute_subkind
-                    if sub == "FWD":
-                        self._forward(node)
-                    elif sub == "BWD":
-                        a.faults.maybe_fire("bwd", a.iteration)
-                        self._backward(node, loss_fn, split=False)
-                    elif sub == "BWD_I":
-                        a.faults.maybe_fire("bwd", a.iteration)
-                        self._backward(node, loss_fn, split=True)
-                    elif sub == "BWD_W":
-                        self._backward_weight(node)
-                elif kind == SEND:
-                    self._send(node)
-                elif kind == RECV:
-                    self._recv(node)
-                elif kind == REDUCE:
-                    self._all_reduce(node)
-                elif kind == REDUCE_SCATTER:
-                    self._reduce_scatter(node)
-                elif kind == ALL_GATHER:
-                    self._all_gather(node)
-                elif kind == A2A:
-                    self._all_to_all(node)
-                elif kind == UPD:
-                    self._update(node)
-                self._record(node)
-                if self.cuda and uid == a._last_compute_uid:
-                    tail0 = torch.cuda.Event(enable_timing=True)
-                    tail0.record(self._stream(node))
-                if a.time_nodes:
-                    host_ms = (time.perf_counter() - t_node) * 1e3
-                    if self.cuda:
-                        ev1 = torch.cuda.Event(enable_timing=True)
-                        ev1.record(self._stream(node))
-                        timed.append((uid, node.compute_subkind or kind, ev0, ev1, host_ms))
-                    else:
-                        timed.append((uid, node.compute_subkind or kind, None, None, host_ms))
-            if label is not None and not a.no_nvtx:
-                torch.cuda.nvtx.range_pop()
+        self._tail0 = None
+        plan = a.native_plan(self) if (self.cuda and not a.profile_nodes) else None
+        if plan is not None:
+            # the C++ executor owns stream switching, event waits/records, NVTX ranges and per-node timing;
+            # Python only runs the bodies
+            nodes = [self.dag.nodes[uid] for uid in a.order]
+            host_ms = [0.0] * len(nodes) if a.time_nodes else None
+            plan.set_timing(bool(a.time_nodes))
+
+            def body(i: int) -> None:
+                t_node = time.perf_counter() if host_ms is not None else 0.0
+                self._dispatch(nodes[i], loss_fn)
+                if host_ms is not None:
+                    host_ms[i] = (time.perf_counter() - t_node) * 1e3
+
+            plan.run(body)
+            if a.time_nodes:
+                dev_ms = plan.elapsed()
+                timed = [(n.uid, n.compute_subkind or n.node_kind, dev_ms[i], host_ms[i]) for i, n in enumerate(nodes)]
+        else:
+            for uid in a.order:
+                node = self.dag.nodes[uid]
+                label = None
+                if self.cuda and (not a.no_nvtx or a.profile_nodes):
+                    label = _node_label(node)
+                    if not a.no_nvtx:
+                        torch.cuda.nvtx.range_push(label)
+                rf = torch.profiler.record_function(label) if (a.profile_nodes and label) else _NullCtx()
+                with rf, (torch.cuda.stream(self._stream(node)) if self.cuda else _NullCtx()):
+                    self._wait_preds(node)
+                    t_node = time.perf_counter()
+                    if a.time_nodes and self.cuda:
+                        ev0 = torch.cuda.Event(enable_timing=True)
+                        ev0.record(self._stream(node))
+                    self._dispatch(node, loss_fn)
+                    self._record(node)
+                    if a.time_nodes:
+                        host = (time.perf_counter() - t_node) * 1e3
+                        if self.cuda:
+                            ev1 = torch.cuda.Event(enable_timing=True)
+                            ev1.record(self._stream(node))
+                            timed.append((uid, node.compute_subkind or node.node_kind, (ev0, ev1), host))
+                        else:
+                            timed.append((uid, node.compute_subkind or node.node_kind, None, host))
+                if label is not None and not a.no_nvtx:
+                    torch.cuda.nvtx.range_pop()
         for ws in self._works.values():
             for w in ws:
                 w.wait()
@@ -535,10 +565,10 @@ class DagExecutor:
                     cur.wait_stream(s)
             for s in a._channel_streams.values():
                 cur.wait_stream(s)
-            if a._last_compute_uid is not None:
+            if self._tail0 is not None:
                 tail1 = torch.cuda.Event(enable_timing=True)
                 tail1.record(cur)
-                a._tail_events = (tail0, tail1)
+                a._tail_events = (self._tail0, tail1)
         a.last_losses = self.losses
         host_s = time.perf_counter() - t0
         a.last_host_time_s = host_s
@@ -546,14 +576,77 @@ class DagExecutor:
             if self.cuda:
                 torch.cuda.synchronize()
             per_kind: dict = {}
-            for uid, k, e0, e1, host_ms in timed:
+            for uid, k, dev, host in timed:
                 rec = per_kind.setdefault(k, {"count": 0, "device_ms": 0.0, "host_ms": 0.0})
                 rec["count"] += 1
-                rec["host_ms"] += host_ms
-                if e0 is not None:
-                    rec["device_ms"] += e0.elapsed_time(e1)
+                rec["host_ms"] += host
+                if isinstance(dev, tuple):
+                    rec["device_ms"] += dev[0].elapsed_time(dev[1])
+                elif dev is not None:
+                    rec["device_ms"] += float(dev)
             a.node_times = per_kind
         return {"losses": self.losses, "host_time_s": host_s}
+
+    def _dispatch(self, node: TrainingDAGNode, loss_fn: Callable) -> None:
+        """Body of one node; the caller has made the node's stream current and enqueued its event waits."""
+        a = self.a
+        kind = node.node_kind
+        if kind == COMPUTE:
+            sub = node.compute_subkind
+            if sub == "FWD":
+                self._forward(node)
+            elif sub == "BWD":
+                a.faults.maybe_fire("bwd", a.iteration)
+                self._backward(node, loss_fn, split=False)
+            elif sub == "BWD_I":
+                a.faults.maybe_fire("bwd", a.iteration)
+                self._backward(node, loss_fn, split=True)
+            elif sub == "BWD_W":
+                self._backward_weight(node)
+        elif kind == SEND:
+            self._send(node)
+        elif kind == RECV:
+            self._recv(node)
+        elif kind == REDUCE:
+            self._all_reduce(node)
+        elif kind == REDUCE_SCATTER:
+            self._reduce_scatter(node)
+        elif kind == ALL_GATHER:
+            self._all_gather(node)
+        elif kind == A2A:
+            self._all_to_all(node)
+        elif kind == UPD:
+            self._update(node)
+        if self.cuda and node.uid == a._last_compute_uid:
+            self._tail0 = torch.cuda.Event(enable_timing=True)
+            self._tail0.record(self._stream(node))
+
+    def static_waits(self, order: list) -> tuple:
+        """The plan behind ``_wait_preds``: per node the stream it runs on and the earlier nodes on other streams
+        that it waits for (order between pipeline messages is host issue order only)."""
+        index = {uid: i for i, uid in enumerate(order)}
+        streams, stream_ids, node_stream, waits = [], {}, [], []
+        for uid in order:
+            s = self._stream(self.dag.nodes[uid])
+            if id(s) not in stream_ids:
+                stream_ids[id(s)] = len(streams)
+                streams.append(s)
+            node_stream.append(stream_ids[id(s)])
+        for i, uid in enumerate(order):
+            node = self.dag.nodes[uid]
+            p2p = node.node_kind in (SEND, RECV)
+            w = set()
+            for e in self.dag.in_edges(uid):
+                j = index.get(e.src_uid)
+                if j is None or j >= i:
+                    continue
+                pn = self.dag.nodes[e.src_uid]
+                if p2p and pn.node_kind in (SEND, RECV) and e.dep_kind == "temporal":
+                    continue
+                if node_stream[j] != node_stream[i]:
+                    w.add(j)
+            waits.append(sorted(w))
+        return streams, node_stream, waits
 
     # ------------------------------------------------------------ compute
     def _forward(self, node: TrainingDAGNode) -> None:

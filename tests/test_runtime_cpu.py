@@ -334,3 +334,55 @@ def test_optimizer_mapping_rejects_what_the_kernels_cannot_do():
         _adam_config(torch.optim.SGD, {"lr": 0.1})
     with pytest.raises(ValueError):
         _adam_config(torch.optim.Adam, {"amsgrad": True})
+
+
+def test_launch_plan_matches_the_dag_edges_and_the_native_module_validates_plans():
+    """The static plan handed to the C++ executor: a node waits exactly for its earlier predecessors that run on
+    another stream (order between pipeline messages excepted), and the extension module rejects a malformed plan."""
+    import importlib.util
+
+    import pytest
+    import torch
+
+    from piper_b200 import piper_setup
+    from piper_b200.compiler.builders import build_1f1b_schedule
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.ops import native
+    from piper_b200.runtime.actor import DagExecutor
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    x = torch.randint(0, cfg.vocab_size, (4, 32))
+    sched = [{"op": "place", "filter": {"PP": 0}, "devices": [0], "stream": "pp_stream"},
+             {"op": "replicate", "filter": {"PP": 0}, "devices": [0], "reduce_stream": "dp_stream",
+              "gather_stream": "gather_stream", "shard_grads": True, "shard_params": True, "bucket_size": 1},
+             {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 2}] + build_1f1b_schedule(1, 2)
+    actor = piper_setup(Transformer, (cfg, 32, 1), optim_fn=torch.optim.Adam, example_inputs=[x], example_outputs=x,
+                        model_dtype=torch.float32, const_attrs=Transformer.const_attrs(cfg, 32),
+                        schedule_directives=sched, device="cpu")
+    ex = DagExecutor(actor)
+    fake = {}
+    ex._stream = lambda node: fake.setdefault(node.stream, object())      # one stand-in stream per logical stream
+    streams, node_stream, waits = ex.static_waits(actor.order)
+    assert len(streams) == len({actor.dag.nodes[u].stream for u in actor.order}) >= 2
+    index = {u: i for i, u in enumerate(actor.order)}
+    n_cross = 0
+    for i, uid in enumerate(actor.order):
+        want = set()
+        for e in actor.dag.in_edges(uid):
+            j = index[e.src_uid]
+            assert j < i                                                   # the dispatch order respects every edge
+            if actor.dag.nodes[e.src_uid].stream != actor.dag.nodes[uid].stream:
+                want.add(j)
+        assert set(waits[i]) == want, uid
+        n_cross += len(want)
+    assert n_cross > 0
+
+    path = native.lib_path().with_name("piper_plan.so")
+    if path.exists():
+        spec = importlib.util.spec_from_file_location("piper_plan", str(path))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        with pytest.raises(ValueError):
+            mod.PlanExecutor(0, [0], [0, 0], [[1], []], ["a", "b"], False)     # waits for a later node
+        with pytest.raises(ValueError):
+            mod.PlanExecutor(0, [0], [0, 3], [[], []], ["a", "b"], False)      # unknown stream

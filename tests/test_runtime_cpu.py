@@ -1,4 +1,5 @@
 """Harness, coordinator / health monitoring, checkpointing, visualisation and trace merging on CPU."""
+import importlib.util
 import json
 import os
 import subprocess
@@ -211,6 +212,53 @@ def test_artifact_dry_run_and_schedule_generator(tmp_path):
     assert out.stdout.count("test_harness.py") == 4 and "pretrain_gpt.py" in out.stdout
     rows = list(__import__("csv").DictReader(open(next(tmp_path.glob("*/results.csv")))))
     assert len(rows) == 8 and {r["schedule"] for r in rows} == {"1f1b", "interleaved_1f1b", "zerobubble", "dualpipev"}
+
+
+def test_artifact_backends_and_log_parsers(tmp_path, monkeypatch):
+    """ssh backend: one command per node for a baseline, one on the head node for this framework; log parsers
+    of the three baselines and of the harness CSV."""
+    spec = importlib.util.spec_from_file_location("e2e_eval_mod", ROOT / "artifact" / "e2e_eval.py")
+    ev = importlib.util.module_from_spec(spec)
+    sys.modules["e2e_eval_mod"] = ev
+    spec.loader.exec_module(ev)
+    for k, v in {"SSH_KEY": "k.pem", "HEAD_PUBLIC_IP": "1.2.3.4", "HEAD_PRIVATE_IP": "10.0.0.1",
+                 "WORKER1_PRIVATE_IP": "10.0.0.2"}.items():
+        monkeypatch.setenv(k, v)
+    be = ev.SshBackend(gpus_per_node=4)
+    exp = ev.Experiment("scalability", "pp4_dp2", "9B", pp=4, dp=2, micro_batch=4, num_microbatches=8)
+    assert be.layout(exp) == (2, 4)
+    lines = be.dry_run_lines("megatron", exp, ev.baseline_command("megatron", exp))
+    assert len(lines) == 2 and "NODE_RANK=1" in lines[1] and "ProxyCommand" in lines[1] and "--node-rank=1" in lines[1]
+    assert "--master-addr=10.0.0.1" in lines[0] and "--nnodes=2" in lines[0]
+    assert len(be.dry_run_lines("piper", exp, ["python", "x.py"])) == 1
+    big = ev.Experiment("scalability", "pp8_dp4", "9B", pp=8, dp=4)
+    with pytest.raises(RuntimeError):
+        be.dry_run_lines("megatron", big, ev.baseline_command("megatron", big))
+    docker = ev.LocalBackend(image="img:1", cuda_visible_devices="0,1")
+    line = docker.dry_run_lines("megatron", exp, ev.baseline_command("megatron", exp))[0]
+    assert line.startswith("docker run") and "device=0,1" in line and "img:1" in line
+
+    log = tmp_path / "m.log"
+    log.write_text(" elapsed time per iteration (ms): 1000.0 | x\n elapsed time per iteration (ms): 3000.0 |\n"
+                   "[Rank 0] (after 2 iterations) memory (MB) | allocated: 1 | max allocated: 2048.0 |\n")
+    r = ev.parse_log("megatron", log)
+    assert r["iter_time_mean_s"] == pytest.approx(2.0) and r["iter_time_std_s"] == pytest.approx(1.0)
+    assert r["peak_memory_gb"] == "2.00" and not r["oom"]
+    log.write_text("\x1b[32m[rank0] step: 1  loss: 9.0  memory: 10.50GiB(13%)  tps: 1,000  mfu: 1%\x1b[0m\n"
+                   "[rank1] step: 1  loss: 9.0  memory: 11.00GiB(13%)  tps: 1,000\n")
+    r = ev.parse_log("torchtitan", log, tokens_per_iter=4000)
+    assert r["iter_time_mean_s"] == pytest.approx(2.0) and r["peak_memory_gb"] == "10.50/11.00"
+    log.write_text("[step 0] loss=1 time=0.500s\npeak memory rank 0: 3.0 GB\ntorch.OutOfMemoryError: CUDA out of memory\n")
+    r = ev.parse_log("deepspeed", log)
+    assert r["iter_time_mean_s"] == pytest.approx(0.5) and r["oom"] and r["peak_memory_gb"] == "3.00"
+    m = tmp_path / "results.csv"
+    m.write_text("dp_rank,iter_time_mean_s,iter_time_std_s,peak_memory_pp0_gb\n0,0.4,0.01,5.0\n1,0.5,0.02,5.5\n")
+    r = ev.parse_log("piper", tmp_path / "none.log", m)
+    assert r["iter_time_mean_s"] == pytest.approx(0.5) and "0:5.50" in r["peak_memory_gb"]
+    rows = [ev.Result(system="piper", sweep="s", name="a", model="9M", schedule="1f1b", pp=1, dp=1, ep=False, zero=0,
+                      micro_batch=1, num_microbatches=1, seq_len=8, gpus=1, global_batch=1, tokens_per_s=10.0)]
+    out = ev.write_results(tmp_path, rows)
+    assert out.is_file() and (tmp_path / "s.svg").is_file()
 
 
 def test_baseline_runners_dry_run_and_padded_bmm_hook():

@@ -35,7 +35,7 @@ def add_common_args(p: argparse.ArgumentParser, default_schedule: str) -> None:
     p.add_argument("--iters", type=int, default=3)
     p.add_argument("--iteration-sleep", type=float, default=0.0)
     p.add_argument("--activation-checkpointing", action="store_true", default=False)
-    p.add_argument("--nsight", action="store_true", default=False, help="accepted for compatibility; use nsys on the job")
+    p.add_argument("--nsight", action="store_true", default=False, help="start every rank under `nsys profile` (one report per rank under <out-root>/nsight_reports)")
     p.add_argument("--viz", action="store_true", default=False, help="save schedule and per-rank DAG visualisations")
     p.add_argument("--temp-dir", default="/tmp/piper/tmp")
     p.add_argument("--use-inductor", action=argparse.BooleanOptionalAction, default=False,

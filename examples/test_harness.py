@@ -124,7 +124,8 @@ def _run_test_module(args, test_args, profile_dir) -> list:
     _, mod = _load_test_file(args.test_file)
     ns = mod.parse_args(test_args)
     coord = Coordinator(schedule_directives_file=ns.schedule_directives_file, hang_timeout=args.hang_timeout,
-                        kill_on_hang=args.hang_timeout is not None)
+                        kill_on_hang=args.hang_timeout is not None, nsight=bool(getattr(ns, "nsight", False)),
+                        nsight_dir=str(Path(args.out_root) / "nsight_reports"))
     extras = {"temp_dir": args.temp_dir, "profile_dir": str(profile_dir) if profile_dir else ""}
     job = coord.run_program(_rank_main, (str(Path(args.test_file).resolve()), list(test_args), extras))
     return [r for r in job.results if r]

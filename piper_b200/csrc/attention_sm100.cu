@@ -38,31 +38,9 @@
 namespace piper {
 namespace {
 
-// 0: waits suspend inside mbarrier.try_wait; 1: waits poll mbarrier.test_wait (set from PIPER_ATTN_SPIN).
-__constant__ int c_attn_spin;
-
-// Optional timeline of one CTA of the backward kernels (a debugging aid, off unless attn_set_trace installs a
-// buffer of 16 * 256 timestamps): event kind k of iteration it, written by block (0, 0, 0) only.
-__device__ unsigned long long* g_attn_trace;
-
-__device__ __forceinline__ void trace_event(int kind, int it) {
-  unsigned long long* t = g_attn_trace;
-  if (t != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && it < 256) {
-    unsigned long long now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    t[kind * 256 + it] = now;
-  }
-}
-
-// Bounded wait on an mbarrier phase (see mbar_wait in ptx.cuh), in either of the two forms above.
+// Bounded wait on an mbarrier phase (see mbar_wait in ptx.cuh).
 __device__ __forceinline__ bool await(uint64_t* bar, uint32_t parity, int* status) {
-  if (c_attn_spin == 0) return mbar_wait(bar, parity, status);
-  for (uint32_t i = 0; i < kMaxMbarPolls; ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 4095u) == 4095u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
-  }
-  if (status != nullptr) atomicCAS(status, 0, kStatusMbarTimeout);
-  return false;
+  return mbar_wait(bar, parity, status);
 }
 
 // The same for a whole warp, with one outcome for all its lanes: a lane that gave up while its neighbours saw
@@ -592,7 +570,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         const int ti = (MODE == 0) ? it : 2 * xb + it % tiles_per_head;      // streamed tile index
         const int yrow = static_cast<int>(tok0) + ti * 64;
         uint8_t* yb = smem + L::Y_OFF;
-        trace_event(8 * MODE + 0, it);               // streamed tile requested
         mbar_arrive_expect_tx(&bars->y_full[st], 2 * L::Y_TILE);
         for (int h = 0; h < L::HALVES; ++h) {
           uint8_t* y1 = yb + L::y_off(st, 0, h);
@@ -643,7 +620,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         if (a_next < s_next && mbar_test_wait(&bars->t_full, a_next & 1)) {
           const int jt = a_next;
           const int st = jt % L::Y_STAGES;
-          trace_event(8 * MODE + 2, jt);             // accumulation MMAs issued
           tc_fence_after();
           const uint64_t dy1 = umma_desc_sw128(smem_u32(smem + L::Y_OFF + L::y_off(st, 0, 0)), L::HALF_STRIDE, 1024);
           const uint64_t dy2 = umma_desc_sw128(smem_u32(smem + L::Y_OFF + L::y_off(st, 1, 0)), L::HALF_STRIDE, 1024);
@@ -671,7 +647,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           const int ss = it & 1;
           if (mbar_test_wait(&bars->y_full[st], (it / L::Y_STAGES) & 1) &&
               mbar_test_wait(&bars->s_empty[ss], ((it >> 1) & 1) ^ 1)) {
-            trace_event(8 * MODE + 1, it);           // S'/dP' MMAs issued
             tc_fence_after();
             const uint32_t y1 = smem_u32(smem + L::Y_OFF + L::y_off(st, 0, 0));
             const uint32_t y2 = smem_u32(smem + L::Y_OFF + L::y_off(st, 1, 0));
@@ -751,7 +726,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
         if (!await_all(&bars->v_full[st], (it >> 1) & 1, status)) { ok = false; break; }
       }
       if (!await_all(&bars->s_full[st], (it >> 1) & 1, status)) { ok = false; break; }
-      if (threadIdx.x == 0) trace_event(8 * MODE + 3, it);     // S'/dP' seen complete
       tc_fence_after();
       // Causal mask is needed only where the streamed tile overlaps the
       // stationary rows: element (x row, y col) is kept iff key <= query.
@@ -793,16 +767,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
           pw[i] = pack_bf16x2(p[0], p[1]);
           dw[i] = pack_bf16x2(d[0], d[1]);
         }
-        if (threadIdx.x == 0) trace_event(8 * MODE + 4, it);   // P'/dS' computed
         // the tiles were last read by the MMAs of the previous iteration
         if (it >= 1 && !await_all(&bars->t_empty, (it - 1) & 1, status)) { ok = false; break; }
-        if (threadIdx.x == 0) trace_event(8 * MODE + 5, it);   // tile buffer free
         if (MODE == 1) store_row_chunk_sw128(smem + L::P_OFF, row, c * 4, pw);
         store_row_chunk_sw128(smem + L::DS_OFF, row, c * 4, dw);
       }
       fence_proxy_async_smem();
       warp_arrive(&bars->t_full, lane);
-      if (threadIdx.x == 0) trace_event(8 * MODE + 6, it);     // P'/dS' published
     }
     if (ok && await_all(&bars->acc_full, 0, status)) {
       tc_fence_after();
@@ -843,15 +814,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv_x,   // box {64, 12
   }
 }
 
-void configure_waits() {
-  static bool done = false;
-  if (done) return;
-  const char* env = getenv("PIPER_ATTN_SPIN");
-  const int spin = (env != nullptr && env[0] == '1') ? 1 : 0;
-  cudaMemcpyToSymbol(c_attn_spin, &spin, sizeof(int));
-  done = true;
-}
-
 template <typename K>
 int set_smem(K kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess
@@ -868,7 +830,6 @@ int attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int Hq, int H
              float softmax_scale, int* status, cudaStream_t st) {
   if (S % 128 != 0 || Hq % Hkv != 0 || (hd != 64 && hd != 128)) return -1;
   if (B == 0) return 0;
-  configure_waits();
   const long long T = static_cast<long long>(B) * S;
   const uint64_t W = static_cast<uint64_t>(Hq + 2 * Hkv) * hd;
   CUtensorMap tm;
@@ -974,16 +935,11 @@ static int attn_bwd_impl(const void* qkv, const void* out, const void* d_out, co
   return kv_ok && q_ok ? 0 : -3;
 }
 
-int attn_set_trace(unsigned long long* buf) {
-  return cudaMemcpyToSymbol(g_attn_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -3;
-}
-
 int attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,
              void* d_qkv, int B, int S, int Hq, int Hkv, int hd, float softmax_scale, int* status,
              cudaStream_t st) {
   if (S % 128 != 0 || Hq % Hkv != 0 || (hd != 64 && hd != 128)) return -1;
   if (B == 0) return 0;
-  configure_waits();
   if (hd == 128)
     return attn_bwd_impl<128>(qkv, out, d_out, lse, delta, d_qkv, B, S, Hq, Hkv, softmax_scale, status, st);
   return attn_bwd_impl<64>(qkv, out, d_out, lse, delta, d_qkv, B, S, Hq, Hkv, softmax_scale, status, st);

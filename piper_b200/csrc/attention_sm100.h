@@ -15,10 +15,6 @@ int attn_fwd(const void* qkv, void* out, float* lse, int B, int S, int Hq, int H
 
 // d_qkv has the layout of qkv and is fully overwritten.  delta is scratch of
 // B*Hq*S floats provided by the caller.
-// Debugging aid: installs (or with nullptr removes) a device buffer of 16 * 256 timestamps into which block
-// (0, 0, 0) of the backward kernels records when each role reached each step of each iteration.
-int attn_set_trace(unsigned long long* buf);
-
 int attn_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,
              void* d_qkv, int B, int S, int Hq, int Hkv, int hd, float softmax_scale, int* status,
              cudaStream_t st);

@@ -271,15 +271,6 @@ void attn_fwd(const Tensor& qkv, Tensor out, Tensor lse, int64_t B, int64_t S, i
            "attn_fwd");
 }
 
-void attn_set_trace(const OptTensor& buf) {
-  unsigned long long* p = nullptr;
-  if (buf.has_value()) {
-    TORCH_CHECK(buf->scalar_type() == at::kLong && buf->is_cuda() && buf->numel() >= 16 * 256, "trace buffer: CUDA int64[4096]");
-    p = reinterpret_cast<unsigned long long*>(buf->data_ptr<int64_t>());
-  }
-  check_rc(piper::attn_set_trace(p), "attn_set_trace");
-}
-
 void attn_bwd(const Tensor& qkv, const Tensor& out, const Tensor& dout, const Tensor& lse, Tensor delta,
               Tensor dqkv, int64_t B, int64_t S, int64_t Hq, int64_t Hkv, int64_t hd, double scale,
               Tensor status) {
@@ -319,7 +310,6 @@ TORCH_LIBRARY(piper_c, m) {
   m.def("add_bf16", &add_bf16);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
-  m.def("attn_set_trace", &attn_set_trace);
   register_moe_ops(m);
   register_fused_ops(m);
 }

@@ -127,11 +127,16 @@ def piper_setup(model_class, model_args=(), model_kwargs: Optional[dict] = None,
     """Compile ``model_class(*model_args)`` under the schedule and build this process's actor.
 
     ``example_inputs`` / ``example_outputs`` hold one replica's batch for a step (all microbatches
-    concatenated on dim 0); they are loaded as the first step's data.  ``use_inductor``, ``nsight``,
-    ``pg``, ``temp_dir`` and ``pp_outer`` are accepted for call-site compatibility and have no effect:
-    there is no Inductor/Triton path and no Ray placement group in this runtime.
+    concatenated on dim 0); they are loaded as the first step's data.  ``use_inductor``, ``pg``,
+    ``temp_dir`` and ``pp_outer`` are accepted for call-site compatibility and have no effect: there is no
+    Inductor/Triton path and no Ray placement group in this runtime.  ``nsight`` belongs to the launcher
+    (``Coordinator(nsight=...)`` starts every rank under ``nsys profile``, the counterpart of the reference's
+    per-actor ``runtime_env``, ``src/actor.py:57-64``); here it only checks that the process is being profiled.
     """
-    del pg, nsight, temp_dir, pp_outer
+    del pg, temp_dir, pp_outer
+    if nsight and not os.environ.get("NSYS_PROFILING_SESSION_ID"):
+        logger.warning("nsight=True but this process does not run under nsys: start the job through "
+                       "Coordinator(nsight=True) or the harness's --nsight")
     if model_dtype not in (torch.bfloat16, torch.float32):
         raise ValueError(f"model_dtype must be bfloat16 or float32, got {model_dtype}")
     if use_inductor:

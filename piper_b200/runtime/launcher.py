@@ -12,11 +12,19 @@ every rank has finished or failed.  In addition every rank touches a heartbeat f
 a rank whose heartbeat is older than ``hang_timeout`` seconds while its process is alive is reported as
 hung, and the job is ended when ``kill_on_hang`` is set - the bounded hang detection that the reference
 names as its next milestone.  All failures are produced and observed on the host.
+
+Nsight Systems: with ``nsight`` set (``True`` or a dict of ``nsys profile`` options) every rank is started as
+``nsys profile -o <dir>/piper_rank<r> ... python -m piper_b200.runtime.launcher <payload>`` instead of a spawned
+child, one report per rank, as the reference does per Ray actor (``src/actor.py:57-64,81``).  The executor's
+NVTX ranges (one per DAG node) label the timeline.  A missing ``nsys`` binary is an error, not a silent no-op.
 """
 from __future__ import annotations
 
 import os
+import shutil
 import socket
+import subprocess
+import sys
 import tempfile
 import time
 import traceback
@@ -64,6 +72,52 @@ def _rank_entry(rank: int, world: int, port: int, env: dict, fn: Callable, args:
         raise
 
 
+NSIGHT_DEFAULTS = {"t": "cuda,nvtx,osrt,cublas,cudnn", "cuda-memory-usage": "true", "cuda-graph-trace": "node",
+                   "force-overwrite": "true"}
+
+
+def nsight_prefix(rank: int, report_dir: str, options: Optional[dict] = None, nsys: str = "nsys") -> list:
+    """``nsys profile`` command prefix of one rank; ``options`` override or extend the defaults (a one-letter key
+    becomes ``-k value``, a longer one ``--key=value``; ``None`` drops a default)."""
+    opts = dict(NSIGHT_DEFAULTS)
+    opts.update(options or {})
+    opts.setdefault("o", os.path.join(report_dir, f"piper_rank{rank}"))
+    cmd = [nsys, "profile"]
+    for k, v in opts.items():
+        if v is None:
+            continue
+        cmd += [f"-{k}", str(v)] if len(k) == 1 else [f"--{k}={v}"]
+    return cmd
+
+
+class _CommandRank:
+    """A rank started as a command (under ``nsys``), with the part of ``multiprocessing.Process`` the watch loop uses."""
+
+    def __init__(self, cmd: list, log_path: str) -> None:
+        self._log = open(log_path, "w", encoding="utf-8")
+        self._p = subprocess.Popen(cmd, stdout=self._log, stderr=subprocess.STDOUT)
+
+    def start(self) -> None:
+        pass
+
+    def is_alive(self) -> bool:
+        return self._p.poll() is None
+
+    @property
+    def exitcode(self):
+        return self._p.poll()
+
+    def terminate(self) -> None:
+        self._p.terminate()
+
+    def join(self, timeout: Optional[float] = None) -> None:
+        try:
+            self._p.wait(timeout)
+        except subprocess.TimeoutExpired:
+            self._p.kill()
+        self._log.close()
+
+
 @dataclass
 class JobResult:
     ok: bool
@@ -83,7 +137,8 @@ class Coordinator:
     """Starts the ranks of one job and watches over them."""
 
     def __init__(self, schedule_directives_file: Optional[str] = None, world_size: Optional[int] = None,
-                 hang_timeout: Optional[float] = None, kill_on_hang: bool = False, poll_s: float = 0.2) -> None:
+                 hang_timeout: Optional[float] = None, kill_on_hang: bool = False, poll_s: float = 0.2,
+                 nsight=None, nsight_dir: Optional[str] = None) -> None:
         self.schedule_file = schedule_directives_file
         self.stage_devices = None
         if schedule_directives_file is not None:
@@ -96,6 +151,8 @@ class Coordinator:
         self.kill_on_hang = kill_on_hang
         self.poll_s = poll_s
         self.standby = os.environ.get(STANDBY_ENV, "0") == "1"
+        self.nsight = ({} if nsight is True else dict(nsight)) if nsight else None
+        self.nsight_dir = nsight_dir
 
     def _rank_env(self, rank: int) -> dict:
         env = {"PIPER_WORLD_SIZE": str(self.world_size)}
@@ -110,8 +167,12 @@ class Coordinator:
         ctx = mp.get_context("spawn")
         out_dir = tempfile.mkdtemp(prefix="piper_job_")
         port = free_port()
-        procs = [ctx.Process(target=_rank_entry, args=(r, self.world_size, port, self._rank_env(r), fn, args, out_dir))
-                 for r in range(self.world_size)]
+        if self.nsight is not None:
+            procs = self._nsight_ranks(fn, args, port, out_dir)
+        else:
+            procs = [ctx.Process(target=_rank_entry,
+                                 args=(r, self.world_size, port, self._rank_env(r), fn, args, out_dir))
+                     for r in range(self.world_size)]
         for p in procs:
             p.start()
         t0 = time.time()
@@ -164,6 +225,24 @@ class Coordinator:
             raise JobFailed(job)
         return job
 
+    def _nsight_ranks(self, fn: Callable, args: Any, port: int, out_dir: str) -> list:
+        import cloudpickle
+
+        nsys = shutil.which(str(self.nsight.pop("nsys", "nsys")))
+        if nsys is None:
+            raise RuntimeError("nsight was requested but no `nsys` binary is on PATH")
+        report_dir = self.nsight_dir or os.path.join(os.getcwd(), "nsight_reports")
+        os.makedirs(report_dir, exist_ok=True)
+        procs = []
+        for r in range(self.world_size):
+            payload = os.path.join(out_dir, f"payload_rank{r}.pkl")
+            with open(payload, "wb") as f:
+                cloudpickle.dump((r, self.world_size, port, self._rank_env(r), fn, args, out_dir), f)
+            cmd = nsight_prefix(r, report_dir, self.nsight, nsys) + [sys.executable, "-m", __name__, payload]
+            procs.append(_CommandRank(cmd, os.path.join(report_dir, f"piper_rank{r}.log")))
+        logger.info(f"ranks run under nsys; reports in {report_dir}")
+        return procs
+
     @staticmethod
     def _failure_text(out_dir: str, rank: int, code) -> str:
         f = os.path.join(out_dir, f"result_rank{rank}.pt")
@@ -183,3 +262,10 @@ class Coordinator:
 
 # name kept for code written against the reference
 PiperProgramCoordinator = Coordinator
+
+
+if __name__ == "__main__":           # one rank started as a command (under nsys): the payload names everything
+    import pickle
+
+    with open(sys.argv[1], "rb") as _f:
+        _rank_entry(*pickle.load(_f))

@@ -261,6 +261,36 @@ def test_artifact_backends_and_log_parsers(tmp_path, monkeypatch):
     assert out.is_file() and (tmp_path / "s.svg").is_file()
 
 
+def _nsight_job(args, pg=None):
+    return {"rank": int(os.environ["RANK"]), "profiled": os.environ.get("FAKE_NSYS_OUT", "")}
+
+
+def test_coordinator_runs_ranks_under_nsys(tmp_path, monkeypatch):
+    """With nsight set, every rank is started as `nsys profile ... python -m piper_b200.runtime.launcher payload`;
+    a stand-in `nsys` records its options and runs the command."""
+    from piper_b200.runtime.launcher import Coordinator, nsight_prefix
+
+    fake = tmp_path / "bin" / "nsys"
+    fake.parent.mkdir()
+    fake.write_text("#!/bin/bash\n[ \"$1\" = profile ] || exit 9\nshift\nopts=()\n"
+                    "while [[ \"$1\" == -* ]]; do if [[ \"$1\" == --* ]]; then opts+=(\"$1\"); shift; "
+                    "else opts+=(\"$1 $2\"); out=\"$2\"; shift 2; fi; done\n"
+                    "printf '%s\\n' \"${opts[@]}\" > \"$out.opts\"\nFAKE_NSYS_OUT=\"$out\" exec \"$@\"\n")
+    fake.chmod(0o755)
+    monkeypatch.setenv("PATH", f"{fake.parent}:{os.environ['PATH']}")
+    reports = tmp_path / "reports"
+    job = Coordinator(world_size=2, nsight={"t": "cuda,nvtx", "cuda-graph-trace": None}, nsight_dir=str(reports)
+                      ).run_program(_nsight_job, None, timeout=120)
+    assert job.ok and [r["rank"] for r in job.results] == [0, 1]
+    assert job.results[1]["profiled"] == str(reports / "piper_rank1")
+    opts = (reports / "piper_rank0.opts").read_text()
+    assert "-t cuda,nvtx" in opts and "--force-overwrite=true" in opts and "cuda-graph-trace" not in opts
+    assert nsight_prefix(3, "/r")[:2] == ["nsys", "profile"] and "/r/piper_rank3" in nsight_prefix(3, "/r")
+    monkeypatch.setenv("PATH", "/nonexistent")
+    with pytest.raises(RuntimeError, match="nsys"):
+        Coordinator(world_size=1, nsight=True).run_program(_nsight_job, None)
+
+
 def test_baseline_runners_dry_run_and_padded_bmm_hook():
     """Megatron runner builds its command without Megatron; DeepSpeed runner reports the missing package; the
     TorchTitan hook's padded batched-matmul experts equal a per-expert loop."""

@@ -40,12 +40,32 @@ __device__ __forceinline__ void adam_vec(float4& g, float4& w, float4& mm, float
   }
 }
 
-// vectors per thread per trip; all peer loads of a trip are issued before the first use
-__host__ __device__ constexpr int unroll_for(int dp) { return dp <= 2 ? 4 : (dp <= 4 ? 2 : 1); }
+// vectors per thread per trip; every load of a trip (peer gradients, accumulator, optimizer state) is issued
+// before the first use, so one trip costs one round of memory latency, remote and local overlapped
+__host__ __device__ constexpr int unroll_for(int dp, bool acc, bool fin) {
+  return dp <= 2 ? (fin ? (acc ? 2 : 3) : 4) : (dp <= 4 ? ((acc && fin) ? 1 : 2) : 1);
+}
 
-// DP > 0: group size known at compile time (peer loops fully unrolled); DP == 0: any size.
-template <int DP>
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ void store_update(const float4& w, const float4& mm, const float4& vv, float* master,
+                                             float* m, float* v, float* shard_grads, __nv_bfloat16* shard_params,
+                                             __nv_bfloat16* const* peer_params, int dp, long long so, long long fo,
+                                             long long i) {
+  reinterpret_cast<float4*>(master + so)[i] = w;
+  reinterpret_cast<float4*>(m + so)[i] = mm;
+  reinterpret_cast<float4*>(v + so)[i] = vv;
+  if (shard_grads != nullptr) reinterpret_cast<float4*>(shard_grads + so)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  uint2 packed;
+  packed.x = pack_bf16x2(w.x, w.y);
+  packed.y = pack_bf16x2(w.z, w.w);
+  reinterpret_cast<uint2*>(shard_params + so)[i] = packed;
+  if (peer_params != nullptr)
+    for (int p = 0; p < dp; ++p) reinterpret_cast<uint2*>(peer_params[p] + fo)[i] = packed;
+}
+
+// DP > 0: group size known at compile time (peer loops fully unrolled); DP == 0: any size.  ACC / FIN mirror the
+// run-time flags `accumulate` / `final_step` for DP > 0 (the DP == 0 kernel reads the flags).
+template <int DP, bool ACC, bool FIN>
+__global__ void __launch_bounds__(kThreads, 2)
 zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restrict__ shard_grads,
                    float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                    __nv_bfloat16* __restrict__ shard_params, __nv_bfloat16* const* __restrict__ peer_params,
@@ -55,7 +75,7 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
   if (abort[0] != 0) return;
   const int dp = DP > 0 ? DP : dp_rt;
   constexpr int NP = DP > 0 ? DP : 1;
-  constexpr int U = unroll_for(NP);
+  constexpr int U = unroll_for(NP, ACC, FIN);
   const long long stride_thr = static_cast<long long>(gridDim.x) * kThreads;
   const long long first = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
   for (int s = 0; s < t.n; ++s) {
@@ -70,14 +90,19 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
 #pragma unroll
       for (int p = 0; p < NP; ++p) gsrc[p] = peer_grads[(my_rank + 1 + p) % NP] + fo;   // own copy last
       for (long long i0 = first; i0 < nvec; i0 += stride_thr * U) {
-        float4 g[U][NP], acc[U];
+        float4 g[U][NP], acc[ACC ? U : 1], w[FIN ? U : 1], mm[FIN ? U : 1], vv[FIN ? U : 1];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const long long i = i0 + u * stride_thr;
           if (i < nvec) {
 #pragma unroll
             for (int p = 0; p < NP; ++p) g[u][p] = ld_stream_f4(gsrc[p] + 4 * i);
-            if (accumulate) acc[u] = ld_stream_f4(shard_grads + so + 4 * i);
+            if (ACC) acc[ACC ? u : 0] = ld_stream_f4(shard_grads + so + 4 * i);
+            if (FIN) {
+              w[FIN ? u : 0] = ld_stream_f4(master + so + 4 * i);
+              mm[FIN ? u : 0] = ld_stream_f4(m + so + 4 * i);
+              vv[FIN ? u : 0] = ld_stream_f4(v + so + 4 * i);
+            }
           }
         }
 #pragma unroll
@@ -89,28 +114,18 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
           for (int p = 1; p < NP; ++p) {
             sum.x += g[u][p].x; sum.y += g[u][p].y; sum.z += g[u][p].z; sum.w += g[u][p].w;
           }
-          if (accumulate) { sum.x += acc[u].x; sum.y += acc[u].y; sum.z += acc[u].z; sum.w += acc[u].w; }
+          if (ACC) {
+            const float4 a = acc[ACC ? u : 0];
+            sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+          }
           // this rank's own copy of the piece is read by nobody else: clear it for the next accumulation
           reinterpret_cast<float4*>(const_cast<float*>(gsrc[NP - 1]))[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (!final_step) {
+          if (!FIN) {
             reinterpret_cast<float4*>(shard_grads + so)[i] = sum;
-            continue;
-          }
-          float4 w = reinterpret_cast<const float4*>(master + so)[i];
-          float4 mm = reinterpret_cast<const float4*>(m + so)[i];
-          float4 vv = reinterpret_cast<const float4*>(v + so)[i];
-          adam_vec(sum, w, mm, vv, h);
-          reinterpret_cast<float4*>(master + so)[i] = w;
-          reinterpret_cast<float4*>(m + so)[i] = mm;
-          reinterpret_cast<float4*>(v + so)[i] = vv;
-          if (shard_grads != nullptr) reinterpret_cast<float4*>(shard_grads + so)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-          uint2 packed;
-          packed.x = pack_bf16x2(w.x, w.y);
-          packed.y = pack_bf16x2(w.z, w.w);
-          reinterpret_cast<uint2*>(shard_params + so)[i] = packed;
-          if (peer_params != nullptr) {
-#pragma unroll
-            for (int p = 0; p < NP; ++p) reinterpret_cast<uint2*>(peer_params[p] + fo)[i] = packed;
+          } else {
+            adam_vec(sum, w[FIN ? u : 0], mm[FIN ? u : 0], vv[FIN ? u : 0], h);
+            store_update(w[FIN ? u : 0], mm[FIN ? u : 0], vv[FIN ? u : 0], master, m, v, shard_grads, shard_params,
+                         peer_params, NP, so, fo, i);
           }
         }
       }
@@ -134,16 +149,7 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
         float4 mm = reinterpret_cast<const float4*>(m + so)[i];
         float4 vv = reinterpret_cast<const float4*>(v + so)[i];
         adam_vec(sum, w, mm, vv, h);
-        reinterpret_cast<float4*>(master + so)[i] = w;
-        reinterpret_cast<float4*>(m + so)[i] = mm;
-        reinterpret_cast<float4*>(v + so)[i] = vv;
-        if (shard_grads != nullptr) reinterpret_cast<float4*>(shard_grads + so)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        uint2 packed;
-        packed.x = pack_bf16x2(w.x, w.y);
-        packed.y = pack_bf16x2(w.z, w.w);
-        reinterpret_cast<uint2*>(shard_params + so)[i] = packed;
-        if (peer_params != nullptr)
-          for (int p = 0; p < dp; ++p) reinterpret_cast<uint2*>(peer_params[p] + fo)[i] = packed;
+        store_update(w, mm, vv, master, m, v, shard_grads, shard_params, peer_params, dp, so, fo, i);
       }
     }
   }
@@ -156,6 +162,25 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
       __threadfence_system();
       for (int p = 0; p < dp; ++p) st_release_sys(peer_flags[p] + done_off + my_rank, use);
     }
+  }
+}
+
+// Clears the pieces of the full gradient buffer that the peers own (they have read them; this rank's own pieces
+// were cleared by the reduction).  blockIdx.y = owner rank.
+__global__ void __launch_bounds__(kThreads)
+zero_clear_others_kernel(float* __restrict__ grads, ZeroTable t, int my_rank) {
+  const int p = blockIdx.y;
+  if (p == my_rank) return;
+  const long long stride_thr = static_cast<long long>(gridDim.x) * kThreads;
+  const long long first = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+  const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < t.n; ++s) {
+    const long long piece = t.stride[s];
+    long long len = t.padded[s] - static_cast<long long>(p) * piece;
+    len = len < 0 ? 0 : (len > piece ? piece : len);
+    float4* dst = reinterpret_cast<float4*>(grads + t.full_base[s] + static_cast<long long>(p) * piece);
+#pragma unroll 4
+    for (long long i = first; i < len / 4; i += stride_thr) dst[i] = z;
   }
 }
 
@@ -196,19 +221,33 @@ int zero_reduce(const ZeroReduceArgs& a, cudaStream_t st) {
   if (!a.final_step && a.shard_grads == nullptr) return -1;
   auto sp = static_cast<__nv_bfloat16*>(a.shard_params);
   auto pp = reinterpret_cast<__nv_bfloat16* const*>(a.peer_params);
-#define PIPER_ZERO_LAUNCH(DPV)                                                                                   \
-  zero_reduce_kernel<DPV><<<a.num_ctas, kThreads, 0, st>>>(a.peer_grads, a.shard_grads, a.master, a.m, a.v, sp, \
-                                                           pp, a.t, a.my_rank, a.dp, a.accumulate, a.final_step, \
-                                                           a.h, a.peer_flags, a.done_off, a.use, a.cta_counter,  \
-                                                           a.abort)
+#define PIPER_ZERO_LAUNCH_AF(DPV, ACC, FIN)                                                                      \
+  zero_reduce_kernel<DPV, ACC, FIN><<<a.num_ctas, kThreads, 0, st>>>(                                            \
+      a.peer_grads, a.shard_grads, a.master, a.m, a.v, sp, pp, a.t, a.my_rank, a.dp, a.accumulate, a.final_step, \
+      a.h, a.peer_flags, a.done_off, a.use, a.cta_counter, a.abort)
+#define PIPER_ZERO_LAUNCH(DPV)                                        \
+  do {                                                                \
+    if (a.accumulate && a.final_step) PIPER_ZERO_LAUNCH_AF(DPV, true, true);        \
+    else if (a.accumulate) PIPER_ZERO_LAUNCH_AF(DPV, true, false);    \
+    else if (a.final_step) PIPER_ZERO_LAUNCH_AF(DPV, false, true);    \
+    else PIPER_ZERO_LAUNCH_AF(DPV, false, false);                     \
+  } while (0)
   switch (a.dp) {
     case 1: PIPER_ZERO_LAUNCH(1); break;
     case 2: PIPER_ZERO_LAUNCH(2); break;
     case 4: PIPER_ZERO_LAUNCH(4); break;
     case 8: PIPER_ZERO_LAUNCH(8); break;
-    default: PIPER_ZERO_LAUNCH(0); break;
+    default: PIPER_ZERO_LAUNCH_AF(0, false, false); break;
   }
+#undef PIPER_ZERO_LAUNCH_AF
 #undef PIPER_ZERO_LAUNCH
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int zero_clear_others(float* grads, const ZeroTable& t, int my_rank, int dp, int num_ctas, cudaStream_t st) {
+  if (dp < 1 || t.n < 0 || num_ctas < 1 || my_rank < 0 || my_rank >= dp) return -1;
+  if (t.n == 0 || dp == 1) return 0;
+  zero_clear_others_kernel<<<dim3(num_ctas, dp), kThreads, 0, st>>>(grads, t, my_rank);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 

@@ -52,6 +52,9 @@ struct ZeroReduceArgs {
 // every rank's full buffer.  The last CTA publishes `use` in the DONE block of every rank.
 int zero_reduce(const ZeroReduceArgs& a, cudaStream_t st);
 
+// Clears every piece of the full gradient buffer that another rank owns (after all ranks have read them).
+int zero_clear_others(float* grads, const ZeroTable& t, int my_rank, int dp, int num_ctas, cudaStream_t st);
+
 // full[piece p of parameter i] = shard of rank p, for every rank p and every parameter except skip_slot
 // (only parameter only_slot when that is >= 0).
 int zero_gather(const void* const* peer_shards, void* full, const ZeroTable& t, int dp, int skip_slot, int only_slot,

@@ -176,7 +176,7 @@ class FusedCollectives:
                         self.num_ctas)
         # nobody reads this rank's gradients any more once every peer is done: clear them for the next chain
         lib.ep_wait(fb.flags_local, DONE_OFF * dp, dp, fb.use, self.timeout_s, status, 12, None)
-        st.flat_grads.zero_()
+        lib.zero_clear_others(st.flat_grads, fb.table, me, dp, self.num_ctas)
         if final:
             st.fused_stepped = True
             if st.params_sharded:

@@ -215,6 +215,9 @@ class PiperActor:
             dtype = slots[0].dtype
             storage = ParamStorage(key, slots, self.device, dtype, mode, self.layout.dp_rank, self.layout.dp_degree,
                                    self.groups.dp_group if self.groups else None, self.adam, self.seed)
+            if ep and ep_degree > 1 and ep.get("groups") and len(ep["groups"]) > 1 and self.groups is not None:
+                # the same expert shard lives in every expert-parallel group: sum its gradients over those replicas
+                storage.replica_group = self.groups.expert_replica_group
         input_meta = [(tuple(gargs[p].shape), gargs[p].dtype) for p in m["input_idxs"]]
         return StageBucket(key=key, gm=gm, n_placeholders=len(phs), input_pos=list(m["input_idxs"]), slots=slots,
                            storage=storage, constants=constants, input_meta=input_meta)
@@ -909,13 +912,14 @@ class DagExecutor:
             st = b.storage
             if st is None or st.numel == 0:
                 continue
+            if st.replica_group is not None and st.flat_grads is not None:
+                dist.all_reduce(st.flat_grads, group=st.replica_group)
             if a.debug_keep_grads:
                 a.last_grads.update(st.snapshot_grads(scale))
             if getattr(st, "fused_stepped", False):
                 st.fused_stepped = False
                 continue
-            ep_scale = scale
-            st.step(ep_scale)
+            st.step(scale)
 
 
 class _Hold:

@@ -89,6 +89,8 @@ class ProcessGroups:
         self._channels: dict = {}
         self._channel_tags: dict = {}
         self._ep_subgroups: dict = {}
+        self.expert_replica_group = None      # ranks that hold the same expert shard (EP groups nested in DP)
+        self.expert_replica_ranks: tuple = ()
         for t in layout._tuples_as_written:
             if len(t) > 1:
                 g = dist.new_group(ranks=list(t), backend=backend, timeout=self.timeout)
@@ -111,6 +113,16 @@ class ProcessGroups:
         self._ep_subgroups[key] = mine
         if mine is not None:
             self.ep_group, self.ep_ranks = mine
+        # Experts are partitioned inside a sub-group and replicated across sub-groups: the ranks at the same
+        # position of every sub-group hold the same experts and must sum their gradients.
+        if len(groups) > 1:
+            if len({len(g) for g in groups}) != 1:
+                raise ValueError(f"shard.devices: expert-parallel groups must have equal sizes, got {groups}")
+            for i in range(len(groups[0])):
+                ranks = [g[i] for g in groups]
+                pg = dist.new_group(ranks=ranks, backend=self.backend, timeout=self.timeout)
+                if self.layout.global_rank in ranks:
+                    self.expert_replica_group, self.expert_replica_ranks = pg, tuple(ranks)
 
     def declare_channels(self, channels: list) -> None:
         """``channels``: sorted list of (rank_a, rank_b, from_stage, to_stage, pass) over the whole job."""

@@ -98,6 +98,7 @@ class ParamStorage:
         self.dp_rank, self.dp_degree, self.dp_group = dp_rank, max(dp_degree, 1), dp_group
         self.adam = adam
         self.step_count = 0
+        self.replica_group = None        # expert shards replicated over expert-parallel groups: summed before the step
         off = 0
         for s in self.slots:
             s.offset = off

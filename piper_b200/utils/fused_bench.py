@@ -90,6 +90,7 @@ def _f1(rank: int, world: int, ranks: list, n: int, timed, rows: list) -> None:
         lib.zero_reduce(gbuf.peer_ptrs, None, master, m, v, shard_p, pbuf.peer_ptrs, table, rank, world, False, True,
                         1e-4, 0.9, 0.95, 1e-8, 0.0, False, u, 1.0, fbuf.peer_ptrs, world, u, counter, abort, ctas)
         lib.ep_wait(flags_local, world, world, u, 30.0, st, 12, None)
+        lib.zero_clear_others(grads, table, rank, world, ctas)
 
     # bytes crossing NVLink per direction and rank: this rank reads its rows of every peer's fp32 gradients
     # (4 B/element) and every peer stores its updated bf16 rows into this rank's parameter buffer (2 B/element)

@@ -211,3 +211,26 @@ def test_expert_parallel_dp2_ep2_matches_single_process(tmp_path):
                 per = want.shape[0] // 2
                 want = want[r["dp_rank"] * per:(r["dp_rank"] + 1) * per]
             assert torch.allclose(g, want, atol=2e-5), (k, float((g - want).abs().max()))
+
+
+def test_expert_groups_nested_in_data_parallel_sum_replica_gradients(tmp_path):
+    """DP4 with two expert-parallel groups of two ranks: ranks 0 and 2 (1 and 3) hold the same experts, so their
+    gradients are summed across the groups; every gradient equals the single-process one."""
+    extra = [{"op": "replicate", "filter": {"PP": 0}, "devices": [0, 1, 2, 3], "reduce_stream": "dp_stream"},
+             {"op": "shard", "filter": {"PP": 0, "EP": "*"}, "devices": [[0, 1], [2, 3]], "stream": "ep_stream"}]
+    sched = _sched([[0, 1, 2, 3]], 1, extra=extra)
+    res = run_ranks(4, _moe_worker, (sched, 1, 4, 4), tmp_path, timeout=600)
+    ref = _moe_reference(4)
+    losses = [l for r in res for l in r["losses"]]
+    assert abs(sum(losses) / len(losses) - ref["loss"]) < 1e-5
+    sliced = 0
+    for r in res:
+        for k, g in r["grads"].items():
+            want = ref["grads"][k]
+            if g.shape != want.shape:
+                per = want.shape[0] // 2
+                i = r["dp_rank"] % 2                      # position inside the expert-parallel group
+                want = want[i * per:(i + 1) * per]
+                sliced += 1
+            assert torch.allclose(g, want, atol=2e-5), (k, r["dp_rank"], float((g - want).abs().max()))
+    assert sliced > 0

@@ -43,7 +43,7 @@ __device__ __forceinline__ void adam_vec(float4& g, float4& w, float4& mm, float
 // vectors per thread per trip; every load of a trip (peer gradients, accumulator, optimizer state) is issued
 // before the first use, so one trip costs one round of memory latency, remote and local overlapped
 __host__ __device__ constexpr int unroll_for(int dp, bool acc, bool fin) {
-  return dp <= 2 ? (fin ? (acc ? 2 : 3) : 4) : (dp <= 4 ? ((acc && fin) ? 1 : 2) : 1);
+  return dp <= 2 ? (fin ? (acc ? 2 : 4) : 4) : (dp <= 4 ? ((acc && fin) ? 1 : 2) : 1);
 }
 
 __device__ __forceinline__ void store_update(const float4& w, const float4& mm, const float4& vv, float* master,
@@ -86,29 +86,43 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
     const long long fo = t.full_base[s] + static_cast<long long>(my_rank) * piece;
     const long long so = t.shard_off[s];
     if (DP > 0) {
-      const float* gsrc[NP];
+      // per-slot base pointers in registers; a parameter has fewer than 2^31 vectors, so the trip index is 32-bit
+      const float4* gsrc[NP];
+      uint2* pdst[NP];
 #pragma unroll
-      for (int p = 0; p < NP; ++p) gsrc[p] = peer_grads[(my_rank + 1 + p) % NP] + fo;   // own copy last
-      for (long long i0 = first; i0 < nvec; i0 += stride_thr * U) {
+      for (int p = 0; p < NP; ++p) {
+        gsrc[p] = reinterpret_cast<const float4*>(peer_grads[(my_rank + 1 + p) % NP] + fo);   // own copy last
+        pdst[p] = (FIN && peer_params != nullptr) ? reinterpret_cast<uint2*>(peer_params[(my_rank + 1 + p) % NP] + fo)
+                                                  : nullptr;
+      }
+      float4* own = const_cast<float4*>(gsrc[NP - 1]);
+      float4* sg4 = (ACC || !FIN) ? reinterpret_cast<float4*>(shard_grads + so) : nullptr;
+      float4* w4 = reinterpret_cast<float4*>(master + so);
+      float4* m4 = reinterpret_cast<float4*>(m + so);
+      float4* v4 = reinterpret_cast<float4*>(v + so);
+      uint2* sp2 = reinterpret_cast<uint2*>(shard_params + so);
+      const unsigned n32 = static_cast<unsigned>(nvec);
+      const unsigned step32 = static_cast<unsigned>(stride_thr);
+      for (unsigned i0 = static_cast<unsigned>(first); i0 < n32; i0 += step32 * U) {
         float4 g[U][NP], acc[ACC ? U : 1], w[FIN ? U : 1], mm[FIN ? U : 1], vv[FIN ? U : 1];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const long long i = i0 + u * stride_thr;
-          if (i < nvec) {
+          const unsigned i = i0 + u * step32;
+          if (i < n32) {
 #pragma unroll
-            for (int p = 0; p < NP; ++p) g[u][p] = ld_stream_f4(gsrc[p] + 4 * i);
-            if (ACC) acc[ACC ? u : 0] = ld_stream_f4(shard_grads + so + 4 * i);
+            for (int p = 0; p < NP; ++p) g[u][p] = ld_stream_f4(reinterpret_cast<const float*>(gsrc[p] + i));
+            if (ACC) acc[ACC ? u : 0] = ld_stream_f4(reinterpret_cast<const float*>(sg4 + i));
             if (FIN) {
-              w[FIN ? u : 0] = ld_stream_f4(master + so + 4 * i);
-              mm[FIN ? u : 0] = ld_stream_f4(m + so + 4 * i);
-              vv[FIN ? u : 0] = ld_stream_f4(v + so + 4 * i);
+              w[FIN ? u : 0] = ld_stream_f4(reinterpret_cast<const float*>(w4 + i));
+              mm[FIN ? u : 0] = ld_stream_f4(reinterpret_cast<const float*>(m4 + i));
+              vv[FIN ? u : 0] = ld_stream_f4(reinterpret_cast<const float*>(v4 + i));
             }
           }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const long long i = i0 + u * stride_thr;
-          if (i >= nvec) continue;
+          const unsigned i = i0 + u * step32;
+          if (i >= n32) continue;
           float4 sum = g[u][0];
 #pragma unroll
           for (int p = 1; p < NP; ++p) {
@@ -119,13 +133,26 @@ zero_reduce_kernel(const float* const* __restrict__ peer_grads, float* __restric
             sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
           }
           // this rank's own copy of the piece is read by nobody else: clear it for the next accumulation
-          reinterpret_cast<float4*>(const_cast<float*>(gsrc[NP - 1]))[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          own[i] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (!FIN) {
-            reinterpret_cast<float4*>(shard_grads + so)[i] = sum;
+            sg4[i] = sum;
           } else {
-            adam_vec(sum, w[FIN ? u : 0], mm[FIN ? u : 0], vv[FIN ? u : 0], h);
-            store_update(w[FIN ? u : 0], mm[FIN ? u : 0], vv[FIN ? u : 0], master, m, v, shard_grads, shard_params,
-                         peer_params, NP, so, fo, i);
+            float4& wu = w[FIN ? u : 0];
+            float4& mu = mm[FIN ? u : 0];
+            float4& vu = vv[FIN ? u : 0];
+            adam_vec(sum, wu, mu, vu, h);
+            w4[i] = wu;
+            m4[i] = mu;
+            v4[i] = vu;
+            if (ACC) sg4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            uint2 packed;
+            packed.x = pack_bf16x2(wu.x, wu.y);
+            packed.y = pack_bf16x2(wu.z, wu.w);
+            sp2[i] = packed;
+            if (peer_params != nullptr) {
+#pragma unroll
+              for (int p = 0; p < NP; ++p) pdst[p][i] = packed;
+            }
           }
         }
       }

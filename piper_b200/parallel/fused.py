@@ -83,6 +83,9 @@ class _FusedBucket:
         self.full_grads = symm("grads", st.numel, torch.float32)
         self.full_params = None if st.params_sharded else symm("params", st.numel, st.dtype)
         self.alloc = symm
+        if any(stride >= 2 ** 33 for _, stride in table):
+            raise ValueError(f"bucket {st.key}: a parameter piece of 2^33 elements or more exceeds the kernels' 32-bit "
+                             "vector index")
         t = torch.tensor([[s.offset for s in st.slots], [sh for sh, _ in table], [stride for _, stride in table],
                           [(s.numel + 63) // 64 * 64 for s in st.slots]], dtype=torch.int64)
         self.table = t.to(dev)
@@ -112,7 +115,7 @@ class FusedCollectives:
             logger.warning("data-parallel group spans hosts: peer memory is unavailable, using the NCCL lowering")
             return None
         self = cls(actor, float(os.environ.get("PIPER_PEER_TIMEOUT_S", "30")),
-                   int(os.environ.get("PIPER_F1_CTAS", "128")))
+                   int(os.environ.get("PIPER_F1_CTAS", "296")))
         for b in actor.buckets.values():
             st = b.storage
             if st is not None and st.mode in ("allreduce", "zero2", "zero3") and st.numel > 0 \

@@ -78,16 +78,21 @@ __device__ __forceinline__ Tile resolve_tile(int t, const int* tile_prefix, cons
     r.group = 0;
     return r;
   }
-  const int mt = t % total_m_tiles;
-  r.n0 = (t / total_m_tiles) * BN;
-  int lo = 0, hi = p.num_groups;          // largest g with tile_prefix[g] <= mt
+  // Column tiles of one row tile are consecutive, and row tiles are walked expert by expert (all sources of an
+  // expert together): the CTAs of a wave share their A tiles and a few experts' weights through L2, so both
+  // operands stream from DRAM once.  (Row tiles fastest re-read every row once per column tile.)
+  (void)total_m_tiles;
+  const int mt = t / tiles_n;
+  r.n0 = (t % tiles_n) * BN;
+  int lo = 0, hi = p.num_groups;          // largest q with tile_prefix[q] <= mt
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
     if (tile_prefix[mid] <= mt) lo = mid; else hi = mid;
   }
-  r.group = lo;
-  r.expert = lo % p.experts;
-  r.m0 = p.g_start[lo] + (mt - tile_prefix[lo]) * BM;
+  const int sources = p.num_groups / p.experts;
+  r.expert = lo / sources;                 // tile_prefix is ordered (expert, source)
+  r.group = (lo % sources) * p.experts + r.expert;
+  r.m0 = p.g_start[r.group] + (mt - tile_prefix[lo]) * BM;
   return r;
 }
 
@@ -123,9 +128,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     int acc = 0;
-    for (int g = 0; g < p.num_groups; ++g) {
-      tile_prefix[g] = acc;
-      acc += p.g_len[g] / BM;
+    for (int q = 0; q < p.num_groups; ++q) {           // q = expert * sources + source; group = source * experts + expert
+      tile_prefix[q] = acc;
+      acc += p.g_len[(q % sources) * p.experts + q / sources] / BM;
     }
     tile_prefix[p.num_groups] = acc;
   }

@@ -12,7 +12,7 @@
 //
 // The structure is that of the dense kernel (gemm_sm100.cu): persistent
 // CTAs, TMA producer warp, single-thread tcgen05.mma issuer, two TMEM
-// accumulators, four epilogue warps; only the tile -> coordinate mapping
+// accumulators, eight epilogue warps; only the tile -> coordinate mapping
 // differs and is computed on the device from the group table, because the
 // row counts are produced by the router on the GPU.  Expert weights are read
 // through a 3-D tensor map (k, n, expert).  No multicast; bounded waits.
@@ -31,7 +31,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;
 constexpr int B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int MN_BOX_BYTES = 64 * BK * 2;
-constexpr int NUM_THREADS = 256;
+constexpr int NUM_THREADS = 384;     // TMA, MMA, TMEM-allocation and one idle warp, then eight epilogue warps
 constexpr int MAX_GROUPS = 1024;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + (MAX_GROUPS + 1) * 4;
 
@@ -122,7 +122,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->acc_full[a], 1);
-      mbar_init(&bars->acc_empty[a], 4);
+      mbar_init(&bars->acc_empty[a], 8);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
@@ -247,19 +247,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else if (warp >= 4) {
-    const int ew = warp - 4;
+    const int q = warp & 3;                     // TMEM lanes [32q, 32q + 32)
+    const int ch = (warp - 4) >> 2;             // columns [128ch, 128ch + 128) of the tile
     uint32_t local_tile = 0;
     bool ok = true;
     for (int ti = blockIdx.x; ti < num_tiles && ok; ti += gridDim.x) {
       const Tile t = resolve_tile<MODE>(ti, tile_prefix, p, total_m_tiles, tiles_n);
       const int kb_total = k_blocks_of(t);
       const int row_limit = (MODE == kGroupedWgrad) ? p.N : 0x7fffffff;
-      const int row = t.m0 + ew * 32 + lane;
+      const int row = t.m0 + q * 32 + lane;
       const long long c_off = (MODE == kGroupedWgrad) ? static_cast<long long>(t.expert) * p.N * p.K : 0;
       if (kb_total == 0) {
         // expert without rows: nothing to add; a non-accumulating output tile is zero
         if (!p.accumulate && row < row_limit) {
-          for (int j = 0; j < BN && t.n0 + j < out_cols; ++j) {
+          for (int j = ch * 128; j < ch * 128 + 128 && t.n0 + j < out_cols; ++j) {
             if (MODE == kGroupedWgrad) reinterpret_cast<float*>(p.c)[c_off + row * p.ldc + t.n0 + j] = 0.f;
           }
         }
@@ -270,13 +271,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       ++local_tile;
       if (!mbar_wait(&bars->acc_full[acc], acc_ph, p.status)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + acc * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + ch * 128;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        const int col0 = t.n0 + c * 32;
+        const int col0 = t.n0 + ch * 128 + c * 32;
         if (row < row_limit && col0 < out_cols) {
           if (MODE == kGroupedWgrad) {
             float* crow = reinterpret_cast<float*>(p.c) + c_off + row * p.ldc + col0;

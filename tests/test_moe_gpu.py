@@ -123,3 +123,51 @@ def test_grouped_gemm_with_no_rows():
     torch.cuda.synchronize()
     native.check_status()
     assert torch.all(dw == 0.0)
+
+
+@pytest.mark.parametrize("sources,E,N,K", [(3, 4, 512, 192), (2, 8, 320, 256)])
+def test_grouped_gemm_with_groups_from_several_sources(sources, E, N, K):
+    """Rows grouped by (source, local expert) with gaps between the sources' regions, empty groups and ragged
+    output widths: forward, input gradient and weight gradient against per-segment fp32 products."""
+    from piper_b200.ops import native
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    lib, st = native.lib(), native.status_tensor(dev)
+    blocks = torch.randint(0, 4, (sources * E,)).tolist()          # 128-row blocks per group, some empty
+    blocks[1] = 0
+    region = (sum(blocks) // sources + 3) * 128                     # every source's region, with slack
+    g_start, g_len, at = [], [], 0
+    for s in range(sources):
+        at = max(at, s * region)
+        for e in range(E):
+            n = blocks[s * E + e] * 128
+            g_start.append(at)
+            g_len.append(n)
+            at += n
+    R = at + 128
+    gs = torch.tensor(g_start, dtype=torch.int32, device=dev)
+    gl = torch.tensor(g_len, dtype=torch.int32, device=dev)
+    w = (torch.randn(E, N, K, device=dev) * 0.1).to(torch.bfloat16)
+    rows = torch.randn(R, K, device=dev).to(torch.bfloat16)
+    dy = torch.randn(R, N, device=dev).to(torch.bfloat16)
+    out = torch.zeros(R, N, device=dev, dtype=torch.bfloat16)
+    dx = torch.zeros(R, K, device=dev, dtype=torch.bfloat16)
+    dw = torch.zeros(E, N, K, device=dev)
+    lib.grouped_gemm(0, rows, None, w, out, gs, gl, E, N, K, False, st)
+    lib.grouped_gemm(1, None, dy, w, dx, gs, gl, E, N, K, False, st)
+    lib.grouped_gemm(2, rows, dy, None, dw, gs, gl, E, N, K, False, st)
+    torch.cuda.synchronize()
+    native.check_status()
+    want_dw = torch.zeros_like(dw)
+    for g, (a, n) in enumerate(zip(g_start, g_len)):
+        if n == 0:
+            continue
+        e = g % E
+        ref = rows[a:a + n].float() @ w[e].float().t()
+        assert (out[a:a + n].float() - ref).abs().max() <= 2e-2 * ref.abs().max(), g
+        ref = dy[a:a + n].float() @ w[e].float()
+        assert (dx[a:a + n].float() - ref).abs().max() <= 2e-2 * ref.abs().max(), g
+        want_dw[e] += dy[a:a + n].float().t() @ rows[a:a + n].float()
+    assert (dw - want_dw).abs().max() <= 2e-2 * want_dw.abs().max()
+    assert torch.count_nonzero(out[R - 128:]) == 0                  # rows outside every group are not written

@@ -17,7 +17,9 @@ import torch
 import torch.nn as nn
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CANDIDATES = [os.environ.get("PIPER_REFERENCE_DIR", ""), "/root/reference", os.path.join(ROOT, "baseline", "_ref")]
+# the reference checkout: named explicitly, installed for the comparison arm, or a sibling of this repository
+CANDIDATES = [os.environ.get("PIPER_REFERENCE_DIR", ""), os.path.join(os.path.dirname(ROOT), "reference"),
+              os.path.join(ROOT, "baseline", "_ref")]
 
 
 def _reference_root():
@@ -143,7 +145,10 @@ def _schedule(tmp_path, base, builder, ranks, mbs, **kw):
         bs = importlib.import_module("build_schedule")
     finally:
         sys.path.pop(0)
-    with open(os.path.join(REF, "examples", "base-schedules", base)) as f:
+    src = os.path.join(REF, "examples", "base-schedules", base)
+    if not os.path.isfile(src):          # an installed copy has no data files: this repository ships the same names
+        src = os.path.join(ROOT, "examples", "base-schedules", base)
+    with open(src) as f:
         prog = [d for d in json.load(f) if d.get("op") not in ("order", "split")]
     prog.append({"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": mbs})
     prog += getattr(bs, builder)(ranks, mbs, **kw)

@@ -127,6 +127,9 @@ def run_ours(args) -> dict:
     torch.cuda.set_device(local)
     if args.config.startswith("qwen"):
         os.environ.setdefault("PIPER_EP_CAPACITY_FACTOR", "1.5")
+        # the 30B shape is memory-tight: keep the host at most sixteen nodes (stage segments, exchanges)
+        # ahead of the device so that blocks freed after a cross-stream use return to the allocator in time
+        os.environ.setdefault("PIPER_MAX_RUN_AHEAD", "16")
     job = build_job(args.config, n, args.model, args.bucket_mb)
     cfg, pp, dp, mbs = job["cfg"], job["pp"], job["dp"], job["mbs"]
     global_seqs = dp * mbs

@@ -74,6 +74,11 @@ class PlanExecutor {
     }
   }
 
+  // Bound on how far the host may run ahead of the device: before node i is issued the host waits until node
+  // i - n has completed (0: no bound).  Memory that a node frees after use on a second stream returns to the
+  // caching allocator only when the device has passed that use, so an unbounded host keeps more blocks alive.
+  void set_max_ahead(int n) { max_ahead_ = n < 0 ? 0 : n; }
+
   // callback(i) runs the body of node i on the current stream.
   void run(const py::function& callback) {
     const c10::cuda::CUDAStream before = c10::cuda::getCurrentCUDAStream(device_);
@@ -82,6 +87,10 @@ class PlanExecutor {
       for (size_t i = 0; i < nodes_.size(); ++i) {
         const Node& nd = nodes_[i];
         cudaStream_t s = streams_[nd.stream];
+        if (max_ahead_ > 0 && i >= static_cast<size_t>(max_ahead_)) {
+          py::gil_scoped_release release;
+          check(cudaEventSynchronize(done_[i - max_ahead_]), "cudaEventSynchronize");
+        }
         c10::cuda::setCurrentCUDAStream(c10::cuda::getStreamFromExternal(s, device_));
         for (int w : nd.waits) check(cudaStreamWaitEvent(s, done_[w], 0), "cudaStreamWaitEvent");
         if (nvtx_) nvtxRangePushA(nd.label.c_str());
@@ -125,6 +134,7 @@ class PlanExecutor {
   int device_;
   bool nvtx_;
   bool timing_ = false, timed_ = false;
+  int max_ahead_ = 0;
   std::vector<cudaStream_t> streams_;
   std::vector<Node> nodes_;
   std::vector<cudaEvent_t> done_, t0_, t1_;
@@ -141,6 +151,7 @@ PYBIND11_MODULE(piper_plan, m) {
            py::arg("nvtx") = false)
       .def("run", &PlanExecutor::run)
       .def("set_timing", &PlanExecutor::set_timing)
+      .def("set_max_ahead", &PlanExecutor::set_max_ahead)
       .def("elapsed", &PlanExecutor::elapsed)
       .def("__len__", &PlanExecutor::size)
       .def_property_readonly("num_waits", &PlanExecutor::num_waits);

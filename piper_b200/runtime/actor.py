@@ -309,6 +309,7 @@ class PiperActor:
             self._plan = mod.PlanExecutor(self.device.index if self.device.index is not None else
                                           torch.cuda.current_device(), [int(s.cuda_stream) for s in streams],
                                           node_stream, waits, labels, not self.no_nvtx)
+            self._plan.set_max_ahead(int(os.environ.get("PIPER_MAX_RUN_AHEAD", "0")))
         return self._plan
 
     def comm_tail_ms(self) -> float:

@@ -126,7 +126,7 @@ def run_ours(args) -> dict:
     rank = int(os.environ.get("RANK", "0"))
     torch.cuda.set_device(local)
     if args.config.startswith("qwen"):
-        os.environ.setdefault("PIPER_EP_CAPACITY_FACTOR", "1.5")
+        os.environ.setdefault("PIPER_EP_CAPACITY_FACTOR", "1.25")
         # the 30B shape is memory-tight: keep the host at most sixteen nodes (stage segments, exchanges)
         # ahead of the device so that blocks freed after a cross-stream use return to the allocator in time
         os.environ.setdefault("PIPER_MAX_RUN_AHEAD", "16")

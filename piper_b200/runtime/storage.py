@@ -254,12 +254,25 @@ class ParamStorage:
         if self.params_live:
             return
         self.flat_params.untyped_storage().resize_(self.numel * self.flat_params.element_size())
-        if self.dp_degree > 1:
+        if self.row_table is not None:
+            # row-sharded bucket outside a step (checkpoint load, inspection): the step itself gathers with the
+            # peer-memory kernels
+            self.flat_params.copy_(self._rebuild_from_rows())
+        elif self.dp_degree > 1:
             dist.all_gather_into_tensor(self.flat_params, self.shard_params, group=self.dp_group)
         else:
             self.flat_params.copy_(self.shard_params)
         self.params_live = True
         self._register_sinks()
+
+    def _rebuild_from_rows(self) -> torch.Tensor:
+        """Full parameters of a row-sharded bucket: every rank contributes its pieces (a collective)."""
+        mine = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        for _s, a, e, sh in self.owned_pieces():
+            mine[a:e].copy_(self.shard_params[sh:sh + e - a])
+        if self.dp_degree > 1:
+            dist.all_reduce(mine, group=self.dp_group)
+        return mine
 
     def free_params(self, consumer_stream=None) -> None:
         if self.numel == 0 or not self.params_sharded or not self.params_live:
@@ -381,13 +394,7 @@ class ParamStorage:
             return self.flat_params
         flat = torch.empty(self.numel, dtype=self.dtype, device=self.device)
         if self.row_table is not None:
-            # row-sharded: every rank contributes its pieces
-            mine = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
-            for _s, a, e, sh in self.owned_pieces():
-                mine[a:e].copy_(self.shard_params[sh:sh + e - a])
-            if self.dp_degree > 1:
-                dist.all_reduce(mine, group=self.dp_group)
-            return mine
+            return self._rebuild_from_rows()
         if self.dp_degree > 1:
             dist.all_gather_into_tensor(flat, self.shard_params, group=self.dp_group)
         else:

@@ -234,3 +234,31 @@ def test_expert_groups_nested_in_data_parallel_sum_replica_gradients(tmp_path):
                 sliced += 1
             assert torch.allclose(g, want, atol=2e-5), (k, r["dp_rank"], float((g - want).abs().max()))
     assert sliced > 0
+
+
+def _row_gather_worker(rank, world):
+    import torch.distributed as dist
+
+    from piper_b200.runtime.storage import AdamConfig, ParamSlot, ParamStorage
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    shapes = {"a.weight": (300, 16), "norm.weight": (130,), "b.weight": (64, 24)}
+    slots = [ParamSlot(pos=i, fqn=k, shape=v, dtype=torch.float32, requires_grad=True)
+             for i, (k, v) in enumerate(shapes.items())]
+    st = ParamStorage("bucket", slots, torch.device("cpu"), torch.float32, "zero3", rank, world, dist.group.WORLD,
+                      AdamConfig())
+    st.all_gather_params()
+    before = st.flat_params.clone()
+    st.convert_to_rows(lambda name, n, dt: torch.zeros(n, dtype=dt))
+    st.param_users = 1
+    st.free_params()
+    assert not st.params_live
+    st.all_gather_params()                   # outside a step: rebuilt from every rank's row pieces
+    same = bool(torch.equal(st.flat_params, before))
+    full = st.full_param_tensor()
+    dist.destroy_process_group()
+    return same and bool(torch.equal(full, before))
+
+
+def test_row_sharded_bucket_regathers_its_parameters_outside_a_step(tmp_path):
+    assert all(run_ranks(2, _row_gather_worker, (), tmp_path))

@@ -166,6 +166,7 @@ class PiperActor:
         self._last_compute_uid = computes[-1] if computes else None
         self._tail_events = None
         self._plan = None
+        self._release = None
 
     def _bucket_modes(self, dag: TrainingDAG) -> dict:
         modes: dict[str, str] = {}
@@ -496,6 +497,49 @@ class DagExecutor:
         for w in self._works.pop(uid, []):
             w.wait()
 
+    def _release_plan(self) -> tuple:
+        """Static lifetime of every node's outputs: ``release[i]`` lists the producers whose last reader is node
+        ``i`` of the dispatch order, ``readers[p]`` the nodes that read producer ``p``.  Without it every gradient
+        tuple, receive buffer and exchange result of a step would stay referenced until the step ends."""
+        a = self.a
+        if a._release is None:
+            index = {u: i for i, u in enumerate(a.order)}
+            last: dict[str, int] = {}
+            readers: dict[str, list] = {}
+            for i, u in enumerate(a.order):
+                n = self.dag.nodes[u]
+                reads = set(self.dag.data_preds(u))
+                reads.add(n.node_meta.get("from_uid"))
+                reads.add(n.node_meta.get("fwd_uid"))
+                for p in reads:
+                    if p in index and p != u:
+                        last[p] = max(last.get(p, -1), i)
+                        readers.setdefault(p, []).append(u)
+            release: list[list] = [[] for _ in a.order]
+            for p, i in last.items():
+                release[i].append(p)
+            for u, i in index.items():
+                if u not in last:
+                    release[i].append(u)               # read by nobody (gradients of the model inputs)
+                    readers[u] = []
+            a._release = (release, readers)
+        return a._release
+
+    def _release_outputs(self, i: int) -> None:
+        """Drop the outputs whose last reader was node ``i``.  A block that another stream has read goes back to
+        its own stream's pool only after that stream has passed the read."""
+        release, readers = self._release_plan()
+        for p in release[i]:
+            vals = self.outs.pop(p, None)
+            if not vals or not self.cuda:
+                continue
+            ps = self._stream(self.dag.nodes[p])
+            others = {id(s): s for s in (self._stream(self.dag.nodes[u]) for u in readers[p]) if s is not ps}
+            for t in vals:
+                if isinstance(t, torch.Tensor) and t.is_cuda:
+                    for s in others.values():
+                        t.record_stream(s)
+
     # --------------------------------------------------------------- run
     def run(self, loss_fn: Callable) -> dict:
         a = self.a
@@ -522,6 +566,7 @@ class DagExecutor:
             def body(i: int) -> None:
                 t_node = time.perf_counter() if host_ms is not None else 0.0
                 self._dispatch(nodes[i], loss_fn)
+                self._release_outputs(i)
                 if host_ms is not None:
                     host_ms[i] = (time.perf_counter() - t_node) * 1e3
 
@@ -530,7 +575,7 @@ class DagExecutor:
                 dev_ms = plan.elapsed()
                 timed = [(n.uid, n.compute_subkind or n.node_kind, dev_ms[i], host_ms[i]) for i, n in enumerate(nodes)]
         else:
-            for uid in a.order:
+            for pos, uid in enumerate(a.order):
                 node = self.dag.nodes[uid]
                 label = None
                 if self.cuda and (not a.no_nvtx or a.profile_nodes):
@@ -546,6 +591,7 @@ class DagExecutor:
                         ev0.record(self._stream(node))
                     self._dispatch(node, loss_fn)
                     self._record(node)
+                    self._release_outputs(pos)
                     if a.time_nodes:
                         host = (time.perf_counter() - t_node) * 1e3
                         if self.cuda:

@@ -464,3 +464,36 @@ def test_launch_plan_matches_the_dag_edges_and_the_native_module_validates_plans
             mod.PlanExecutor(0, [0], [0, 0], [[1], []], ["a", "b"], False)     # waits for a later node
         with pytest.raises(ValueError):
             mod.PlanExecutor(0, [0], [0, 3], [[], []], ["a", "b"], False)      # unknown stream
+
+
+def test_node_outputs_are_released_after_their_last_reader(monkeypatch):
+    """Gradient tuples, receive buffers and exchange results leave the executor's table as soon as the last node
+    that reads them has been issued, not at the end of the step."""
+    import torch
+
+    from piper_b200 import piper_exec_dag, piper_setup
+    from piper_b200.compiler.builders import build_1f1b_schedule
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.nn import cross_entropy_loss
+    from piper_b200.runtime import actor as actor_mod
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    tok = torch.randint(0, cfg.vocab_size, (8, 33), generator=torch.Generator().manual_seed(0))
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    sched = [{"op": "place", "filter": {"PP": 0}, "devices": [0]}, {"op": "place", "filter": {"PP": 1}, "devices": [0]},
+             {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 8}] + build_1f1b_schedule(1, 8)
+    actor = piper_setup(Transformer, (cfg, 32, 2), optim_fn=torch.optim.Adam, example_inputs=[x], example_outputs=y,
+                        model_dtype=torch.float32, const_attrs=Transformer.const_attrs(cfg, 32),
+                        schedule_directives=sched, device="cpu")
+    seen = []
+    orig = actor_mod.DagExecutor._release_outputs
+
+    def spy(self, i):
+        orig(self, i)
+        seen.append(len(self.outs))
+
+    monkeypatch.setattr(actor_mod.DagExecutor, "_release_outputs", spy)
+    losses = piper_exec_dag(cross_entropy_loss)
+    assert len(losses) == 8 and len(seen) == len(actor.order)
+    assert seen[-1] == 0                               # nothing outlives the step
+    assert max(seen) <= 4 < len(actor.order) // 4      # a few entries at a time, not one per node

@@ -25,6 +25,7 @@ shapes; per-microbatch losses are returned to the caller.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Any, Callable, Optional
@@ -57,6 +58,7 @@ class StageBucket:
     storage: Optional[ParamStorage] = None
     constants: dict = field(default_factory=dict)    # placeholder position -> non-trainable tensor
     input_meta: list = field(default_factory=list)   # (shape, dtype) of the runtime inputs at trace time
+    unsaved_outputs: Optional[list] = None           # output positions whose storage no backward formula keeps
 
     def build_args(self, inputs: list) -> list:
         args: list = [None] * self.n_placeholders
@@ -139,6 +141,7 @@ class PiperActor:
         self.last_host_time_s = 0.0
         self.activation_checkpointing = False   # forward keeps segment inputs only; backward recomputes the segment
         self.debug_keep_grads = False       # tests: keep a scaled copy of the gradients each step
+        self.drop_exchanged = os.environ.get("PIPER_DROP_EXCHANGED", "0") == "1"
         # kernels report expired waits and rejected indices through a per-device status word; it is read once
         # per step through pinned memory (no synchronisation) and a non-zero value of the previous step raises
         self.status_monitor = native.StatusMonitor(device) if device.type == "cuda" else None
@@ -717,6 +720,8 @@ class DagExecutor:
                 # keep only the segment's inputs; the backward node re-runs the segment with autograd on
                 with torch.no_grad():
                     outs = bucket.gm(*bucket.build_args(ins))
+            elif bucket.unsaved_outputs is None and (a.drop_exchanged or not self.cuda):
+                outs = self._forward_tracking_saved(bucket, ins)
             else:
                 outs = bucket.gm(*bucket.build_args(ins))
         finally:
@@ -729,6 +734,54 @@ class DagExecutor:
                                     if isinstance(o, torch.Tensor) and o.is_floating_point()]
         if node.node_meta.get("zero_free_full_params_after") and bucket.storage is not None:
             self._free_params(bucket.storage, node)
+
+    @staticmethod
+    def _forward_tracking_saved(bucket: StageBucket, ins: list):
+        """First run of a segment: note which outputs no backward formula saved (directly or through a view) and
+        which do not alias an input.  Such an output is needed after the forward pass only by whoever reads it,
+        so its memory can go once an exchange has copied it away (``_drop_exchanged``)."""
+        saved: set = set()
+
+        def pack(t):
+            if isinstance(t, torch.Tensor) and t.device.type != "meta":
+                saved.add(t.untyped_storage().data_ptr())
+            return t
+
+        with torch.autograd.graph.saved_tensors_hooks(pack, lambda t: t):
+            outs = bucket.gm(*bucket.build_args(ins))
+        seq = tuple(outs) if isinstance(outs, (tuple, list)) else (outs,)
+        held = saved | {t.untyped_storage().data_ptr() for t in ins if isinstance(t, torch.Tensor)}
+        bucket.unsaved_outputs = [i for i, o in enumerate(seq) if isinstance(o, torch.Tensor) and o.numel() > 0
+                                  and o.untyped_storage().data_ptr() not in held]
+        return outs
+
+    def _drop_exchanged(self, src: str, node: TrainingDAGNode, vals: list, res: tuple) -> None:
+        """The exchanged tensor of a forward segment has been copied to its destination: if the exchange is the
+        segment's only reader and no backward formula kept the tensor, give its memory back now instead of at the
+        segment's backward pass (the tensor object stays as the root of the backward call).
+
+        On CUDA devices this is opt-in (``PIPER_DROP_EXCHANGED=1``): it has only been validated on CPU ranks."""
+        if self.cuda and not self.a.drop_exchanged:
+            return
+        pn = self.dag.nodes[src]
+        ctx = self.fwd_ctx.get(src)
+        if not (pn.node_kind == COMPUTE and pn.compute_subkind == "FWD") or ctx is None or ctx[1] is None:
+            return
+        bucket = self.a.buckets[pn.node_meta["bucket_key"]]
+        ti = node.node_meta.get("a2a_tensor_idx")
+        if ti is None or bucket.unsaved_outputs is None or ti not in bucket.unsaved_outputs:
+            return
+        _release, readers = self._release_plan()
+        forward_readers = [u for u in readers.get(src, [])
+                           if not (self.dag.nodes[u].node_kind == COMPUTE and self.dag.nodes[u].compute_subkind != "FWD")]
+        t, r = vals[ti], res[ti]
+        if forward_readers != [node.uid] or not isinstance(t, torch.Tensor) or not isinstance(r, torch.Tensor):
+            return
+        if r.untyped_storage().data_ptr() == t.untyped_storage().data_ptr() or not t.untyped_storage().resizable():
+            return                                    # passed through (a group of one rank), or memory of a fixed buffer
+        if t.is_cuda:
+            t.record_stream(self._stream(node))
+        t.untyped_storage().resize_(0)
 
     def _output_grads(self, node: TrainingDAGNode):
         """Gradients w.r.t. this segment's outputs from the downstream backward / receive / exchange node.
@@ -946,9 +999,11 @@ class DagExecutor:
         self._wait_work(src)
         ef = self.a.ep_fused
         if ef is not None and ef.supports(node):
-            self.outs[node.uid] = ef.exchange(node, vals)
+            res = ef.exchange(node, vals)
         else:
-            self.outs[node.uid] = exchange_tokens(self, node, vals)
+            res = exchange_tokens(self, node, vals)
+        self.outs[node.uid] = res
+        self._drop_exchanged(src, node, vals, res)
 
     def _update(self, node: TrainingDAGNode) -> None:
         a = self.a

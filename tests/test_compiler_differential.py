@@ -149,9 +149,11 @@ def _schedule(tmp_path, base, builder, ranks, mbs, **kw):
     if not os.path.isfile(src):          # an installed copy has no data files: this repository ships the same names
         src = os.path.join(ROOT, "examples", "base-schedules", base)
     with open(src) as f:
-        prog = [d for d in json.load(f) if d.get("op") not in ("order", "split")]
-    prog.append({"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": mbs})
-    prog += getattr(bs, builder)(ranks, mbs, **kw)
+        prog = json.load(f)
+    if builder is not None:              # otherwise the file's own split and order rows are the program
+        prog = [d for d in prog if d.get("op") not in ("order", "split")]
+        prog.append({"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": mbs})
+        prog += getattr(bs, builder)(ranks, mbs, **kw)
     path = tmp_path / f"{builder}_{base}"
     path.write_text(json.dumps(prog))
     return str(path)
@@ -164,6 +166,9 @@ CASES = [
     ("pp2_dp2_ep2_zero3.json", "build_1f1b_schedule", 2, 2, 2, {}),
     ("pp4_dp2_ep2_interleaved.json", "build_interleaved_1f1b_schedule", 4, 2, 4, {"n_virtual_stages": 2}),
     ("pp4_dp2_ep2_v_placement.json", "build_dualpipev_schedule", 4, 2, 4, {}),
+    ("pp2_dp2_ep2_bucket100.json", "build_1f1b_schedule", 2, 2, 2, {}),
+    ("dp2.json", "build_1f1b_schedule", 1, 1, 2, {}),
+    ("pp2_dp2_ep2_custom_order.json", None, 2, 2, 0, {}),
 ]
 
 

@@ -1,4 +1,5 @@
 """MoE ops on CPU: reference bodies and autograd formulas against a dense formulation."""
+import pytest
 import torch
 
 from piper_b200.ops import moe as M
@@ -90,3 +91,52 @@ def test_qwen3_model_traces_into_pp_and_ep_segments():
     ep_fwd = [n for n in per_dev[0].nodes.values() if n.node_kind == "COMPUTE" and "EP" in n.tag and n.compute_subkind == "FWD"]
     assert all(n.node_meta.get("ep_shard") for n in ep_fwd)
     assert not any(n.node_kind == "REDUCE_COMM" and "EP" in n.tag for n in per_dev[0].nodes.values())
+
+
+@pytest.mark.parametrize("schedule", ["1f1b", "dualpipev", "zerobubble"])
+def test_expert_exchange_buffer_plan_from_the_dispatch_order(schedule):
+    """The slot planner of the peer-memory expert exchanges, on a CPU-compiled plan: every exchange has its four
+    roles, exchanges whose lifetimes overlap in the dispatch order never share a slot or a gradient buffer, the
+    slot count is the largest overlap, and every buffer is handed back by a node of this rank's own order."""
+    from piper_b200 import piper_setup
+    from piper_b200.compiler import builders
+    from piper_b200.models.qwen3 import QWEN3_CONFIGS, PiperQwen3Model
+    from piper_b200.parallel.ep_fused import FusedExpertRuntime, source_capacity
+
+    cfg, seq, mbs = QWEN3_CONFIGS["9M"], 32, 4
+    x = torch.randint(0, cfg.vocab_size, (mbs, seq))
+    stages = 2 if schedule == "dualpipev" else 1
+    sched = [{"op": "place", "filter": {"PP": s}, "devices": [0], "stream": "pp_stream"} for s in range(stages)]
+    sched += [{"op": "shard", "filter": {"PP": s, "EP": "*"}, "devices": [0], "stream": "ep_stream"} for s in range(stages)]
+    sched.append({"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": mbs})
+    sched += {"1f1b": builders.build_1f1b_schedule, "dualpipev": builders.build_dualpipev_schedule,
+              "zerobubble": builders.build_zerobubble_schedule}[schedule](1, mbs)
+    actor = piper_setup(PiperQwen3Model, (cfg, stages, seq), optim_fn=torch.optim.Adam, example_inputs=[x],
+                        example_outputs=x, model_dtype=torch.float32,
+                        const_attrs=PiperQwen3Model.const_attrs(cfg, seq), schedule_directives=sched, device="cpu")
+    rt = FusedExpertRuntime(actor, [0], None, 1.0, 8, 1.25)
+    layers = cfg.n_layers
+    assert len(rt.exchanges) == mbs * layers
+    roles = sorted(k for k, _ in rt.role.values())
+    assert roles.count("F_in") == roles.count("F_out") == roles.count("B_in") == roles.count("B_out") == mbs * layers
+    xs = list(rt.exchanges.values())
+    if schedule != "dualpipev":                          # DualPipeV splits the backward of some microbatches only
+        assert all(x.split_backward == (schedule == "zerobubble") for x in xs)
+    peak = 0
+    for i, a in enumerate(xs):
+        assert 0 <= a.slot < rt.slots and a.first < a.last < len(actor.order)
+        peak = max(peak, sum(1 for b in xs if b.first <= a.first <= b.last))
+        for b in xs[i + 1:]:
+            if not (a.last < b.first or b.last < a.first):
+                assert a.slot != b.slot
+            for span, buf in (("gin_span", "gin_buf"), ("gret_span", "gret_buf")):
+                (a0, a1), (b0, b1) = getattr(a, span), getattr(b, span)
+                if not (a1 < b0 or b1 < a0):
+                    assert getattr(a, buf) != getattr(b, buf)
+    assert rt.slots == peak                               # interval colouring is optimal
+    freed = [act for acts in rt.after.values() for act, _ in acts]
+    assert freed.count("free_recv") == freed.count("free_ret") == freed.count("free_gret") == mbs * layers
+    assert set(rt.after) <= set(actor.order)
+    # capacity: worst case without a factor, the balanced share plus padding reserve with one
+    assert source_capacity(4096, 8, 32, 4, None) >= 4096 * 8
+    assert source_capacity(4096, 8, 32, 4, 1.25) == (10240 + 32 * 127 + 127) // 128 * 128

@@ -497,3 +497,35 @@ def test_node_outputs_are_released_after_their_last_reader(monkeypatch):
     assert len(losses) == 8 and len(seen) == len(actor.order)
     assert seen[-1] == 0                               # nothing outlives the step
     assert max(seen) <= 4 < len(actor.order) // 4      # a few entries at a time, not one per node
+
+
+def test_first_linear_weight_of_a_segment_is_found_for_the_gather_gemm():
+    """ZeRO-3 buckets leave the weight of their segment's first linear layer to the GEMM that gathers it: the
+    lookup returns that weight's slot when the linear call is the weight's only use, and -1 for segments that
+    start with something else (an embedding) or whose parameters are not used by a linear call first."""
+    import torch
+
+    from piper_b200 import piper_setup
+    from piper_b200.models.llama3 import LLAMA_CONFIGS, Transformer
+    from piper_b200.parallel.fused import first_linear_slot
+
+    cfg = LLAMA_CONFIGS["tiny"]
+    x = torch.randint(0, cfg.vocab_size, (4, 32))
+    sched = [{"op": "place", "filter": {"PP": 0}, "devices": [0]}, {"op": "place", "filter": {"PP": 1}, "devices": [0]},
+             {"op": "replicate", "filter": {"PP": 0}, "devices": [0], "bucket_size": 1},
+             {"op": "replicate", "filter": {"PP": 1}, "devices": [0], "bucket_size": 1},
+             {"op": "split", "filter": {}, "dim_name": "MB", "num_microbatches": 2}]
+    actor = piper_setup(Transformer, (cfg, 32, 2), optim_fn=torch.optim.Adam, example_inputs=[x], example_outputs=x,
+                        model_dtype=torch.float32, const_attrs=Transformer.const_attrs(cfg, 32),
+                        schedule_directives=sched, device="cpu")
+    found = {}
+    for key, b in actor.buckets.items():
+        if b.storage is None:
+            continue
+        i = first_linear_slot(b.gm, [s.pos for s in b.storage.slots])
+        found[key] = b.storage.slots[i].fqn if i >= 0 else None
+    assert len(found) > 2                                              # the stages were cut into buckets
+    named = [v for v in found.values() if v]
+    assert named and all(v.endswith("weight") and "norm" not in v and "embed" not in v for v in named)
+    first = next(iter(found))                                          # the first bucket starts with the embedding
+    assert found[first] is None or "tok_embeddings" not in found[first]

@@ -115,7 +115,7 @@ class FusedCollectives:
             logger.warning("data-parallel group spans hosts: peer memory is unavailable, using the NCCL lowering")
             return None
         self = cls(actor, float(os.environ.get("PIPER_PEER_TIMEOUT_S", "30")),
-                   int(os.environ.get("PIPER_F1_CTAS", "296")))
+                   int(os.environ.get("PIPER_F1_CTAS", "128")))
         for b in actor.buckets.values():
             st = b.storage
             if st is not None and st.mode in ("allreduce", "zero2", "zero3") and st.numel > 0 \

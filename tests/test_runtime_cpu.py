@@ -529,3 +529,30 @@ def test_first_linear_weight_of_a_segment_is_found_for_the_gather_gemm():
     assert named and all(v.endswith("weight") and "norm" not in v and "embed" not in v for v in named)
     first = next(iter(found))                                          # the first bucket starts with the embedding
     assert found[first] is None or "tok_embeddings" not in found[first]
+
+
+def test_clock_sampler_with_a_stand_in_nvidia_smi(tmp_path, monkeypatch):
+    """The benchmark's clock record: median SM clock, largest maximum and the set of active event reasons, parsed
+    from the stream of a stand-in ``nvidia-smi``; a machine without the tool yields an empty record."""
+    from baseline.clocks import ClockSampler
+
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/bash\n"
+                    "echo '0, 1500, 1965, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '1, 1700, 1965, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo '0, 1600, 1965, Not Active, Active, Not Active, Active'\n"
+                    "echo 'garbage line'\nsleep 30\n")
+    fake.chmod(0o755)
+    monkeypatch.setenv("PATH", f"{tmp_path}:{os.environ['PATH']}")
+    s = ClockSampler([0, 1])
+    s.start()
+    deadline = time.time() + 10
+    while len(s.rows) < 4 and time.time() < deadline:
+        time.sleep(0.05)
+    rec = s.stop()
+    assert rec == {"sm_mhz": 1600.0, "sm_max_mhz": 1965.0, "reasons": ["hw_thermal_slowdown", "sw_power_cap"],
+                   "samples": 3}
+    monkeypatch.setenv("PATH", str(tmp_path / "nowhere"))
+    s = ClockSampler(0)
+    s.start()
+    assert s.stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
